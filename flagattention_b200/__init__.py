@@ -1,0 +1,5 @@
+"""B200-native drop-in for ``flag_attn.flash_attention``."""
+from .flash import FlashAttentionFunction, check_device_status, flash_attention  # noqa: F401
+
+__all__ = ["flash_attention", "FlashAttentionFunction", "check_device_status"]
+__version__ = "0.1.0"

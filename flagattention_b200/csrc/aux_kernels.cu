@@ -1,0 +1,166 @@
+// Bandwidth-bound helper kernels: dropout keep-mask materialisation and the backward
+// preprocess delta = rowsum(O * dO).
+#include "common.cuh"
+
+namespace b200attn {
+
+// mask[idx] = keep(offset + idx) over the flattened [B, H, M, N] index space; one thread per
+// 16 consecutive elements so stores are 16 bytes wide.
+__global__ void __launch_bounds__(256)
+dropout_mask_kernel(uint8_t* __restrict__ mask, int64_t total, DropoutCtx ctx) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * 16;
+  for (int64_t base = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 16; base < total;
+       base += stride) {
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t idx = base + i;
+      const bool keep = idx < total && dropout_keep(ctx, ctx.offset + static_cast<uint64_t>(idx));
+      w[i >> 2] |= (keep ? 1u : 0u) << (8 * (i & 3));
+    }
+    if (base + 16 <= total && (reinterpret_cast<uintptr_t>(mask + base) & 15) == 0) {
+      *reinterpret_cast<uint4*>(mask + base) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      for (int i = 0; i < 16 && base + i < total; ++i) mask[base + i] = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+    }
+  }
+}
+
+// One warp per row of D elements: lanes read 16-byte vectors, shuffle-reduce, lane 0 writes.
+template <int D, int O_KIND, bool DO_BF16>
+__global__ void __launch_bounds__(256)
+delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __restrict__ delta,
+             int64_t o_sb, int64_t o_sh, int64_t o_sm, int64_t do_sb, int64_t do_sh, int64_t do_sm, int B,
+             int H, int M) {
+  constexpr int VEC = 8;                 // elements per lane per step
+  constexpr int LANES = D / VEC;         // lanes that carry data for one row (2..16)
+  constexpr int ROWS_PER_WARP = 32 / LANES;
+  const int lane = threadIdx.x & 31;
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int sub = lane / LANES;
+  const int col = (lane % LANES) * VEC;
+  const int64_t row_id = static_cast<int64_t>(warp_global) * ROWS_PER_WARP + sub;
+  const int64_t total = static_cast<int64_t>(B) * H * M;
+  float acc = 0.f;
+  if (row_id < total) {
+    const int m = static_cast<int>(row_id % M);
+    const int h = static_cast<int>((row_id / M) % H);
+    const int b = static_cast<int>(row_id / (static_cast<int64_t>(M) * H));
+    const int64_t o_off = b * o_sb + h * o_sh + m * o_sm + col;
+    const int64_t do_off = b * do_sb + h * do_sh + m * do_sm + col;
+    float ov[VEC], gv[VEC];
+    if constexpr (O_KIND == B200ATTN_F32) {
+      const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(o) + o_off);
+      const float4 a = p[0], c = p[1];
+      ov[0] = a.x; ov[1] = a.y; ov[2] = a.z; ov[3] = a.w;
+      ov[4] = c.x; ov[5] = c.y; ov[6] = c.z; ov[7] = c.w;
+    } else {
+      const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(o) + o_off);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2<O_KIND == B200ATTN_BF16>(w[i]);
+        ov[2 * i] = f.x; ov[2 * i + 1] = f.y;
+      }
+    }
+    {
+      const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(d_o) + do_off);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2<DO_BF16>(w[i]);
+        gv[2 * i] = f.x; gv[2 * i + 1] = f.y;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc = fmaf(ov[i], gv[i], acc);
+  }
+#pragma unroll
+  for (int s = LANES / 2; s >= 1; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (row_id < total && (lane % LANES) == 0) delta[row_id] = acc;
+}
+
+template <int D>
+static int launch_delta(const b200attn_tensor* o, int o_dtype, const b200attn_tensor* d_o, int do_dtype,
+                        float* delta, int B, int H, int M, cudaStream_t stream) {
+  constexpr int ROWS_PER_WARP = 32 / (D / 8);
+  const int64_t total = static_cast<int64_t>(B) * H * M;
+  const int64_t warps = (total + ROWS_PER_WARP - 1) / ROWS_PER_WARP;
+  const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
+#define B200ATTN_DELTA(OK, DB)                                                                        \
+  delta_kernel<D, OK, DB><<<blocks, 256, 0, stream>>>(o->ptr, d_o->ptr, delta, o->stride[0],          \
+                                                      o->stride[1], o->stride[2], d_o->stride[0],    \
+                                                      d_o->stride[1], d_o->stride[2], B, H, M)
+  const bool db = do_dtype == B200ATTN_BF16;
+  if (o_dtype == B200ATTN_F32) { if (db) B200ATTN_DELTA(B200ATTN_F32, true); else B200ATTN_DELTA(B200ATTN_F32, false); }
+  else if (o_dtype == B200ATTN_BF16) { if (db) B200ATTN_DELTA(B200ATTN_BF16, true); else B200ATTN_DELTA(B200ATTN_BF16, false); }
+  else { if (db) B200ATTN_DELTA(B200ATTN_F16, true); else B200ATTN_DELTA(B200ATTN_F16, false); }
+#undef B200ATTN_DELTA
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
+}
+
+static int check_vec_tensor(const b200attn_tensor* t, int eb, const char* name) {
+  if (t == nullptr || t->ptr == nullptr) {
+    set_error("%s: null tensor", name);
+    return B200ATTN_EINVAL;
+  }
+  if (t->stride[3] != 1 || reinterpret_cast<uintptr_t>(t->ptr) % 16 != 0 || (t->stride[0] * eb) % 16 ||
+      (t->stride[1] * eb) % 16 || (t->stride[2] * eb) % 16) {
+    set_error("%s: needs feature stride 1 and 16-byte aligned base / strides", name);
+    return B200ATTN_EINVAL;
+  }
+  return B200ATTN_OK;
+}
+
+}  // namespace b200attn
+
+extern "C" int b200attn_dropout_mask(uint8_t* mask, int32_t B, int32_t H, int32_t M, int32_t N,
+                                     float dropout_p, uint64_t seed, uint64_t offset, void* stream) {
+  using namespace b200attn;
+  if (mask == nullptr || B <= 0 || H <= 0 || M <= 0 || N <= 0) {
+    set_error("dropout_mask: bad argument");
+    return B200ATTN_EINVAL;
+  }
+  if (!(dropout_p >= 0.f && dropout_p < 1.f)) {
+    set_error("dropout_mask: dropout_p must be in [0, 1)");
+    return B200ATTN_EINVAL;
+  }
+  const int64_t total = static_cast<int64_t>(B) * H * M * N;
+  const DropoutCtx ctx = make_dropout_ctx(dropout_p, seed, offset);
+  const int64_t threads = (total + 15) / 16;
+  int64_t blocks = (threads + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  dropout_mask_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      mask, total, ctx);
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
+}
+
+extern "C" int b200attn_bwd_delta(const b200attn_tensor* o, int32_t o_dtype, const b200attn_tensor* d_o,
+                                  int32_t do_dtype, float* delta, int32_t B, int32_t H, int32_t M,
+                                  int32_t D, void* stream) {
+  using namespace b200attn;
+  if (delta == nullptr || B <= 0 || H <= 0 || M <= 0) {
+    set_error("bwd_delta: bad argument");
+    return B200ATTN_EINVAL;
+  }
+  int rc = check_vec_tensor(o, o_dtype == B200ATTN_F32 ? 4 : 2, "bwd_delta.o");
+  if (rc) return rc;
+  rc = check_vec_tensor(d_o, 2, "bwd_delta.do");
+  if (rc) return rc;
+  if (do_dtype != B200ATTN_F16 && do_dtype != B200ATTN_BF16) {
+    set_error("bwd_delta: do must be fp16 or bf16");
+    return B200ATTN_EINVAL;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (D) {
+    case 16: return launch_delta<16>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s);
+    case 32: return launch_delta<32>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s);
+    case 64: return launch_delta<64>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s);
+    case 128: return launch_delta<128>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s);
+    default:
+      set_error("bwd_delta: head dimension %d not in {16, 32, 64, 128}", D);
+      return B200ATTN_EINVAL;
+  }
+}

@@ -1,0 +1,133 @@
+// Shared host/device helpers: error reporting, dropout RNG, TMA tensor-map encoding.
+#pragma once
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/b200attn.h"
+
+namespace b200attn {
+
+// --------------------------------------------------------------- host errors
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define B200ATTN_CUDA_OK(expr)                                  \
+  do {                                                          \
+    cudaError_t _e = (expr);                                    \
+    if (_e != cudaSuccess) return ::b200attn::cuda_fail(_e, #expr); \
+  } while (0)
+
+// Encodes a 4-D tiled tensor map over a [B, H, rows, D] tensor of 16-bit elements
+// (dims listed innermost first: D, rows, H, B). `box_cols` x `box_rows` is the tile;
+// `swizzle` is a CUtensorMapSwizzle value. Returns 0 or a negative B200ATTN_E* code.
+int encode_tmap_4d(CUtensorMap* out, const b200attn_tensor& t, int elem_bytes, int64_t B, int64_t H,
+                   int64_t rows, int64_t D, int box_cols, int box_rows, int swizzle,
+                   const char* name);
+
+// Checks the TMA requirements of one operand; returns 0 or B200ATTN_EINVAL.
+int check_tma_operand(const b200attn_tensor& t, int elem_bytes, const char* name);
+
+// Smallest integer threshold T such that a Philox word x (folded to [0, 2^31)) is KEPT iff x > T,
+// equivalent to `float(x) * 4.6566127342e-10f > dropout_p` evaluated in fp32.
+int32_t dropout_keep_threshold(float dropout_p);
+
+// --------------------------------------------------------------- device RNG
+// Philox-4x32 with 6 rounds, keyed by the 64-bit seed, counter = (ctr_lo, ctr_hi, 0, 0);
+// returns output word 0. This is the generator behind the reference's `tl.rand(seed, offs,
+// n_rounds=6)` (flash.py:474-477); only word 0 of each call is consumed there.
+__host__ __device__ __forceinline__ uint32_t philox6_word0(uint32_t seed_lo, uint32_t seed_hi,
+                                                           uint32_t ctr_lo, uint32_t ctr_hi) {
+  constexpr uint32_t KEY_A = 0x9E3779B9u, KEY_B = 0xBB67AE85u;
+  constexpr uint32_t ROUND_A = 0xD2511F53u, ROUND_B = 0xCD9E8D57u;
+  uint32_t c0 = ctr_lo, c1 = ctr_hi, c2 = 0u, c3 = 0u;
+  uint32_t k0 = seed_lo, k1 = seed_hi;
+#pragma unroll
+  for (int r = 0; r < 6; ++r) {
+    const uint64_t pa = static_cast<uint64_t>(ROUND_A) * c0;
+    const uint64_t pb = static_cast<uint64_t>(ROUND_B) * c2;
+    const uint32_t n0 = static_cast<uint32_t>(pb >> 32) ^ c1 ^ k0;
+    const uint32_t n2 = static_cast<uint32_t>(pa >> 32) ^ c3 ^ k1;
+    c1 = static_cast<uint32_t>(pb);
+    c3 = static_cast<uint32_t>(pa);
+    c0 = n0;
+    c2 = n2;
+    k0 += KEY_A;
+    k1 += KEY_B;
+  }
+  return c0;
+}
+
+// Per-launch dropout constants. Element (b,h,m,n) draws counter
+// offset + ((b*H + h)*M + m)*N + n (flash.py:387-391). The reference's kernel does this
+// arithmetic in 32 bits when `offset` fits in int32 (the counter's high word is then 0) and in
+// 64 bits otherwise; `wide` selects between the two.
+struct DropoutCtx {
+  uint32_t seed_lo, seed_hi;
+  uint64_t offset;
+  int32_t keep_threshold;
+  uint32_t wide;
+  float inv_keep;  // 1 / (1 - p)
+};
+
+__host__ inline DropoutCtx make_dropout_ctx(float p, uint64_t seed, uint64_t offset) {
+  DropoutCtx c;
+  c.seed_lo = static_cast<uint32_t>(seed);
+  c.seed_hi = static_cast<uint32_t>(seed >> 32);
+  c.offset = offset;
+  c.keep_threshold = dropout_keep_threshold(p);
+  c.wide = offset >= (1ull << 31) ? 1u : 0u;
+  c.inv_keep = 1.0f / (1.0f - p);
+  return c;
+}
+
+// keep-decision for the element whose exact 64-bit counter is `ctr`.
+__device__ __forceinline__ bool dropout_keep(const DropoutCtx& c, uint64_t ctr) {
+  const uint32_t lo = static_cast<uint32_t>(ctr);
+  const uint32_t hi = c.wide ? static_cast<uint32_t>(ctr >> 32) : 0u;
+  const int32_t x = static_cast<int32_t>(philox6_word0(c.seed_lo, c.seed_hi, lo, hi));
+  const int32_t folded = x ^ (x >> 31);  // x < 0 ? -x - 1 : x
+  return folded > c.keep_threshold;
+}
+
+// ------------------------------------------------------------ small helpers
+__host__ __device__ constexpr int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t u) {
+  if constexpr (BF16) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  } else {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+}
+
+// Status codes written to the optional device status word.
+enum : int32_t {
+  ST_OK = 0,
+  ST_WAIT_TMA = 1,   // a TMA "full" barrier never completed
+  ST_WAIT_MMA = 2,   // a tensor-core completion barrier never completed
+  ST_WAIT_SOFTMAX = 3,
+  ST_WAIT_EMPTY = 4,
+};
+
+__device__ __forceinline__ void report_status(int32_t* status, int32_t code) {
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+}  // namespace b200attn

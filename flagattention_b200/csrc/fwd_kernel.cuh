@@ -1,0 +1,435 @@
+// Forward attention kernel for sm_100a.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row tiles that share every
+// K/V tile brought into shared memory. Roles:
+//   warps 0-3  : softmax + epilogue for query tile 0 (thread r <-> row r, TMEM lane r)
+//   warps 4-7  : softmax + epilogue for query tile 1
+//   warp 8     : tcgen05.mma issuer (one elected lane)
+//   warp 9     : TMA producer (one elected lane)
+// TMEM (512 columns): S0 | S1 (128 fp32 columns each, P aliases the first 64 columns of its S
+// as packed 16-bit pairs) and O0 | O1 (D fp32 columns each).
+// The two tiles ping-pong: while one tile's softmax runs on the CUDA cores the tensor core
+// executes the other tile's GEMMs.
+//
+// Numerics follow the reference kernel (flash.py:442-509): S = QK^T with fp32 accumulation,
+// base-2 online softmax with qk_scale = sm_scale*log2(e), the row sum taken before dropout and
+// before P is rounded to the input type, O normalised once at the end, LSE = m*sm_scale + ln(l).
+// The running maximum is only raised when it grows by more than 2^8 (the accumulators are
+// rescaled then), which leaves O and LSE unchanged up to fp32 rounding.
+#pragma once
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200attn {
+
+template <int D>
+struct TileCfg {
+  static constexpr int BLOCK = 128;                       // rows of a Q tile / a K,V tile
+  static constexpr int CHUNK = D >= 64 ? 64 : D;          // elements per swizzled row segment
+  static constexpr int NCHUNK = D / CHUNK;
+  static constexpr int ROW_BYTES = CHUNK * 2;             // 128 / 64 / 32
+  static constexpr uint32_t UMMA_SWZ = ROW_BYTES == 128 ? SWZ_128B : (ROW_BYTES == 64 ? SWZ_64B : SWZ_32B);
+  static constexpr int TMA_SWZ = ROW_BYTES == 128 ? 3 : (ROW_BYTES == 64 ? 2 : 1);
+  static constexpr int CHUNK_BYTES = BLOCK * ROW_BYTES;   // one [128 x CHUNK] box
+  static constexpr int TILE_BYTES = BLOCK * D * 2;
+  static constexpr int STEPS_PER_CHUNK = CHUNK / 16;
+  // K-major operand (rows = M or N of the MMA, contiguous along the contraction).
+  static constexpr uint64_t KMAJOR_DESC = make_smem_desc_hi(16, 8 * ROW_BYTES, UMMA_SWZ);
+  // MN-major operand (rows = contraction index, contiguous along the MMA's N).
+  static constexpr uint64_t MNMAJOR_DESC = make_smem_desc_hi(CHUNK_BYTES, 8 * ROW_BYTES, UMMA_SWZ);
+};
+
+struct FwdArgs {
+  void* o;
+  float* lse;
+  int64_t o_stride_b, o_stride_h, o_stride_m;
+  int B, Hq, Hkv, M, N, groups;
+  int causal, o_fp32;
+  float sm_scale, qk_scale;
+  DropoutCtx drop;
+  int32_t* status;
+};
+
+template <int D>
+struct FwdSmem {
+  static constexpr int STAGES = D == 128 ? 2 : (D == 64 ? 3 : 4);
+  static constexpr int Q_BYTES = 2 * TileCfg<D>::TILE_BYTES;
+  static constexpr int KV_BYTES = STAGES * TileCfg<D>::TILE_BYTES;
+  static constexpr int BAR_OFFSET = Q_BYTES + 2 * KV_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;  // barriers + alignment slack
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+static constexpr float RESCALE_THRESHOLD = 8.0f;
+
+template <int D, bool BF16, bool DROPOUT>
+__global__ void __launch_bounds__(320, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+           const __grid_constant__ CUtensorMap tmV, const FwdArgs args) {
+  using Cfg = TileCfg<D>;
+  using Sm = FwdSmem<D>;
+  constexpr int STAGES = Sm::STAGES;
+  constexpr int BLOCK = Cfg::BLOCK;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + Sm::Q_BYTES;
+  uint8_t* sV = sK + Sm::KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Sm::BAR_OFFSET);
+  uint64_t* q_full = bars;                  // [2]
+  uint64_t* k_full = bars + 2;              // [STAGES]
+  uint64_t* k_empty = k_full + STAGES;      // [STAGES]
+  uint64_t* v_full = k_empty + STAGES;      // [STAGES]
+  uint64_t* v_empty = v_full + STAGES;      // [STAGES]
+  uint64_t* s_full = v_empty + STAGES;      // [2]
+  uint64_t* p_full = s_full + 2;            // [2]
+  uint64_t* o_full = p_full + 2;            // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_blk = gridDim.x - 1 - blockIdx.x;  // longest (causal) row blocks first
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = h / args.groups;
+  const int m0 = m_blk * 2 * BLOCK;
+  const int P_SEQ = args.N - args.M;
+
+  // Number of K/V tiles each query tile visits.
+  int n_tiles[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int mt = m0 + t * BLOCK;
+    int hi = args.N;
+    if (args.causal) hi = min(args.N, max(0, P_SEQ + mt + BLOCK));
+    n_tiles[t] = mt < args.M ? cdiv(hi, BLOCK) : 0;
+  }
+  const int n_max = max(n_tiles[0], n_tiles[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full[0], 1);
+    mbar_init(&q_full[1], 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 128);
+      mbar_init(&o_full[t], 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&](int32_t code) {
+    report_status(args.status, code);
+    *abort_flag = 1;
+  };
+  auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((++spins & 0xffu) == 0u) {
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+      }
+    }
+  };
+
+  if (warp == 9) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_max > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      for (int t = 0; t < 2; ++t) {
+        if (n_tiles[t] == 0) continue;
+        mbar_expect_tx(&q_full[t], Cfg::TILE_BYTES);
+        for (int c = 0; c < Cfg::NCHUNK; ++c)
+          tma_load_4d(sQ + t * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &q_full[t],
+                      c * Cfg::CHUNK, m0 + t * BLOCK, h, b);
+      }
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j % STAGES;
+        const uint32_t par = ((j / STAGES) & 1) ^ 1;  // first pass over the ring passes at once
+        if (!wait(&k_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
+        mbar_expect_tx(&k_full[st], Cfg::TILE_BYTES);
+        for (int c = 0; c < Cfg::NCHUNK; ++c)
+          tma_load_4d(sK + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmK, &k_full[st],
+                      c * Cfg::CHUNK, j * BLOCK, hk, b);
+        if (!wait(&v_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
+        mbar_expect_tx(&v_full[st], Cfg::TILE_BYTES);
+        for (int c = 0; c < Cfg::NCHUNK; ++c)
+          tma_load_4d(sV + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmV, &v_full[st],
+                      c * Cfg::CHUNK, j * BLOCK, hk, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 8) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_max > 0) {
+      constexpr uint32_t IDESC_QK = make_idesc(BF16, 128, BLOCK, false, false);
+      constexpr uint32_t IDESC_PV = make_idesc(BF16, 128, D, false, true);
+      const uint32_t q_addr = smem_u32(sQ);
+      const uint32_t k_addr = smem_u32(sK);
+      const uint32_t v_addr = smem_u32(sV);
+      auto issue_qk = [&](int t, int st) {
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s) {
+          const uint32_t off = (s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
+                               (s % Cfg::STEPS_PER_CHUNK) * 32;
+          mma_ss(tmem_base + t * BLOCK,
+                 smem_desc(Cfg::KMAJOR_DESC, q_addr + t * Cfg::TILE_BYTES + off),
+                 smem_desc(Cfg::KMAJOR_DESC, k_addr + st * Cfg::TILE_BYTES + off), IDESC_QK,
+                 s > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int t, int st, bool acc) {
+#pragma unroll
+        for (int s = 0; s < BLOCK / 16; ++s) {
+          mma_ts(tmem_base + 2 * BLOCK + t * D, tmem_base + t * BLOCK + s * 8,
+                 smem_desc(Cfg::MNMAJOR_DESC, v_addr + st * Cfg::TILE_BYTES + s * 16 * Cfg::ROW_BYTES),
+                 IDESC_PV, (acc || s > 0) ? 1u : 0u);
+        }
+      };
+      bool ok = true;
+      // Prologue: S_t = Q_t K_0^T for both tiles.
+      if (!wait(&k_full[0], 0)) { fail(ST_WAIT_TMA); ok = false; }
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (n_tiles[t] == 0) continue;
+        if (!wait(&q_full[t], 0)) { fail(ST_WAIT_TMA); ok = false; break; }
+        tc_fence_after();
+        issue_qk(t, 0);
+        tc_commit(&s_full[t]);
+      }
+      if (ok) tc_commit(&k_empty[0]);
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j % STAGES;
+        const int st_next = (j + 1) % STAGES;
+        if (!wait(&v_full[st], (j / STAGES) & 1)) { fail(ST_WAIT_TMA); break; }
+        if (j + 1 < n_max) {
+          if (!wait(&k_full[st_next], ((j + 1) / STAGES) & 1)) { fail(ST_WAIT_TMA); break; }
+        }
+        for (int t = 0; t < 2; ++t) {
+          if (j >= n_tiles[t]) continue;
+          if (!wait(&p_full[t], j & 1)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+          tc_fence_after();
+          issue_pv(t, st, j > 0);
+          if (j + 1 < n_tiles[t]) {
+            issue_qk(t, st_next);
+            tc_commit(&s_full[t]);
+          } else {
+            tc_commit(&o_full[t]);
+          }
+        }
+        if (!ok) break;
+        tc_commit(&v_empty[st]);
+        if (j + 1 < n_max) tc_commit(&k_empty[st_next]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------- softmax + epilogue warps
+    const int t = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const int m_glob = m0 + t * BLOCK + row;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + lane_base + t * BLOCK;
+    const uint32_t tmem_o = tmem_base + lane_base + 2 * BLOCK + t * D;
+    const int nt = n_tiles[t];
+    const float qk_scale = args.qk_scale;
+    // Keys n < lim are visible to this row.
+    const int lim = args.causal ? min(args.N, P_SEQ + m_glob + 1) : args.N;
+    // Tiles j with (j+1)*128 <= full_upto need no masking for any row of the tile.
+    const int full_upto = args.causal ? min(args.N, P_SEQ + m0 + t * BLOCK + 1) : args.N;
+    uint64_t ctr_row = 0;
+    if constexpr (DROPOUT) {
+      ctr_row = args.drop.offset +
+                ((static_cast<uint64_t>(b) * args.Hq + h) * args.M + static_cast<uint64_t>(m_glob)) *
+                    static_cast<uint64_t>(args.N);
+    }
+
+    float m_run = -INFINITY;
+    float l_run = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < nt; ++j) {
+      {
+        const bool w = wait(&s_full[t], j & 1);
+        if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
+      }
+      tc_fence_after();
+      uint32_t s[128];
+      tmem_ld32(tmem_s + 0, s + 0);
+      tmem_ld32(tmem_s + 32, s + 32);
+      tmem_ld32(tmem_s + 64, s + 64);
+      tmem_ld32(tmem_s + 96, s + 96);
+      tmem_wait_ld();
+
+      if ((j + 1) * BLOCK > full_upto) {
+        const int base = j * BLOCK;
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (base + i >= lim) s[i] = 0xff800000u;  // -inf
+      }
+
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
+        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      }
+      const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+
+      // Raise the running maximum only when it moved by more than the threshold.
+      bool want = false;
+      if (m_run == -INFINITY) {
+        m_run = m_new;  // nothing accumulated yet for this row: O row is 0 (or not yet written)
+      } else if ((m_new - m_run) * qk_scale > RESCALE_THRESHOLD) {
+        want = true;
+      }
+      if (__any_sync(0xffffffffu, want)) {
+        // s_full of this iteration also certifies that P V of the previous one has completed,
+        // so O is quiescent here.
+        const float alpha = want ? fast_exp2((m_run - m_new) * qk_scale) : 1.0f;
+        if (want) m_run = m_new;
+        l_run *= alpha;
+#pragma unroll
+        for (int c = 0; c < D; c += 16) {
+          uint32_t o[16];
+          tmem_ld16(tmem_o + c, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st16(tmem_o + c, o);
+        }
+      }
+
+      const float m_eff = (m_run == -INFINITY) ? 0.f : m_run;
+      const float neg_ms = -m_eff * qk_scale;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        float p0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), qk_scale, neg_ms));
+        float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_ms));
+        float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, neg_ms));
+        float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, neg_ms));
+        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+        if constexpr (DROPOUT) {
+          const uint64_t ctr = ctr_row + static_cast<uint64_t>(j * BLOCK + i);
+          if (!dropout_keep(args.drop, ctr + 0)) p0 = 0.f;
+          if (!dropout_keep(args.drop, ctr + 1)) p1 = 0.f;
+          if (!dropout_keep(args.drop, ctr + 2)) p2 = 0.f;
+          if (!dropout_keep(args.drop, ctr + 3)) p3 = 0.f;
+        }
+        s[i / 2 + 0] = pack2<BF16>(p0, p1);
+        s[i / 2 + 1] = pack2<BF16>(p2, p3);
+      }
+      l_run += (sum0 + sum1) + (sum2 + sum3);
+
+      tmem_st32(tmem_s + 0, s + 0);
+      tmem_st32(tmem_s + 32, s + 32);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_full[t]);
+    }
+
+    // ------------------------------------------------------------- epilogue
+    if (ok && nt > 0) {
+      const bool w = wait(&o_full[t], 0);
+      if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; }
+    }
+    if (ok && m_glob < args.M) {
+      const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
+      const float lse = empty ? -INFINITY : m_run * args.sm_scale + logf(l_run);
+      args.lse[(static_cast<int64_t>(b) * args.Hq + h) * args.M + m_glob] = lse;
+    }
+    if (ok) {
+      tc_fence_after();
+      const bool valid = m_glob < args.M;
+      const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
+      float inv = empty ? 0.f : 1.0f / l_run;
+      if constexpr (DROPOUT) inv *= args.drop.inv_keep;
+      const int64_t o_off = b * args.o_stride_b + h * args.o_stride_h +
+                            static_cast<int64_t>(m_glob) * args.o_stride_m;
+#pragma unroll
+      for (int c = 0; c < D; c += 16) {
+        uint32_t o[16];
+        __syncwarp();
+        if (nt > 0) {
+          tmem_ld16(tmem_o + c, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = 0u;
+        }
+        if (valid) {
+          if (args.o_fp32) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(args.o) + o_off + c);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float4 v;
+              v.x = empty ? 0.f : __uint_as_float(o[4 * i + 0]) * inv;
+              v.y = empty ? 0.f : __uint_as_float(o[4 * i + 1]) * inv;
+              v.z = empty ? 0.f : __uint_as_float(o[4 * i + 2]) * inv;
+              v.w = empty ? 0.f : __uint_as_float(o[4 * i + 3]) * inv;
+              dst[i] = v;
+            }
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.o) + o_off + c);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              uint4 v;
+              v.x = pack2<BF16>(empty ? 0.f : __uint_as_float(o[8 * i + 0]) * inv,
+                                empty ? 0.f : __uint_as_float(o[8 * i + 1]) * inv);
+              v.y = pack2<BF16>(empty ? 0.f : __uint_as_float(o[8 * i + 2]) * inv,
+                                empty ? 0.f : __uint_as_float(o[8 * i + 3]) * inv);
+              v.z = pack2<BF16>(empty ? 0.f : __uint_as_float(o[8 * i + 4]) * inv,
+                                empty ? 0.f : __uint_as_float(o[8 * i + 5]) * inv);
+              v.w = pack2<BF16>(empty ? 0.f : __uint_as_float(o[8 * i + 6]) * inv,
+                                empty ? 0.f : __uint_as_float(o[8 * i + 7]) * inv);
+              dst[i] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  if (warp == 8) {
+    if (*abort_flag) {
+      // Give copies that may still be in flight time to land before shared memory is released.
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) {}
+    }
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace b200attn

@@ -1,0 +1,45 @@
+// Host launcher for one head dimension of the forward kernel; each fwd_d*.cu instantiates one D
+// so the variants compile in parallel.
+#pragma once
+#include "fwd_kernel.cuh"
+
+namespace b200attn {
+
+struct FwdLaunch {
+  CUtensorMap tmQ, tmK, tmV;
+  FwdArgs args;
+  dim3 grid;
+  bool bf16, dropout;
+  cudaStream_t stream;
+};
+
+template <int D, bool BF16, bool DROPOUT>
+int launch_fwd_variant(const FwdLaunch& L) {
+  auto kernel = fwd_kernel<D, BF16, DROPOUT>;
+  constexpr int smem = FwdSmem<D>::TOTAL;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  B200ATTN_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+    B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (dev >= 0 && dev < 64) attr_done[dev] = true;
+  }
+  kernel<<<L.grid, 320, smem, L.stream>>>(L.tmQ, L.tmK, L.tmV, L.args);
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
+}
+
+template <int D>
+int launch_fwd_d(const FwdLaunch& L) {
+  if (L.bf16) {
+    return L.dropout ? launch_fwd_variant<D, true, true>(L) : launch_fwd_variant<D, true, false>(L);
+  }
+  return L.dropout ? launch_fwd_variant<D, false, true>(L) : launch_fwd_variant<D, false, false>(L);
+}
+
+int launch_fwd_d16(const FwdLaunch& L);
+int launch_fwd_d32(const FwdLaunch& L);
+int launch_fwd_d64(const FwdLaunch& L);
+int launch_fwd_d128(const FwdLaunch& L);
+
+}  // namespace b200attn

@@ -1,0 +1,208 @@
+"""Host side of ``flash_attention``: the same call contract as ``flag_attn.flash.attention``
+(``flash.py:275-306`` of the reference; autograd function ``flash.py:37-272``), dispatching to the
+sm_100a kernels in ``libb200attn.so``.
+
+Everything here is shape bookkeeping, allocation and the autograd contract; all arithmetic runs in
+the CUDA library. There is no fallback path: a missing library or an unsupported device raises.
+"""
+from __future__ import annotations
+
+import math
+import os
+
+import torch
+
+from . import _lib
+from .rng_state import as_u64, reserve_philox_stream
+from .split_kv import choose_num_splits
+
+__all__ = ["flash_attention", "FlashAttentionFunction", "check_device_status"]
+
+_SUPPORTED_HEAD_DIMS = (16, 32, 64, 128)
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(idx)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[idx] = word
+    return word
+
+
+def check_device_status(device=None) -> None:
+    """Synchronises and raises if any kernel launched so far on ``device`` gave up on a bounded
+    device-side wait (the kernels never spin forever; they record a code and exit instead)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_word(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"b200attn kernel reported device-side wait timeout (code {code})")
+
+
+def _tma_ready(x: torch.Tensor) -> torch.Tensor:
+    """Returns ``x`` or a contiguous copy that satisfies what TMA needs: unit feature stride,
+    16-byte aligned base and strides. The reference only copies when the feature stride is not 1
+    (``flash.py:28-31``); the extra cases cannot be expressed as a tensor map."""
+    esize = x.element_size()
+    ok = x.stride(-1) == 1 and x.data_ptr() % 16 == 0
+    if ok:
+        for dim in range(3):
+            if x.size(dim) > 1 and (x.stride(dim) * esize) % 16 != 0:
+                ok = False
+            if x.size(dim) > 1 and x.stride(dim) <= 0:
+                ok = False
+    return x if ok else x.contiguous()
+
+
+def _vec_ready(x: torch.Tensor) -> torch.Tensor:
+    return _tma_ready(x)
+
+
+class FlashAttentionFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale, dropout_p, return_log_normalizer,
+                return_total_attention, return_seed_offset):
+        Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
+        assert Dq == Dk == Dv, "feature size of q, k, v should be equal"
+        assert Dk in _SUPPORTED_HEAD_DIMS
+        B, H, M, D = q.shape
+        N = k.shape[2]
+        Hk, Hv = k.shape[1], v.shape[1]
+        assert Hk == Hv, "num of heads in k and v should be equal"
+        assert H % Hk == 0, "number of heads in q must be a multiple of that in k & v"
+        if not (q.is_cuda and k.is_cuda and v.is_cuda):
+            raise RuntimeError("flash_attention runs on CUDA tensors only (no CPU fallback)")
+        if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16):
+            raise TypeError("q, k, v must share dtype float16 or bfloat16")
+        if not (q.device == k.device == v.device):
+            raise ValueError("q, k, v must live on the same device")
+        if k.shape[0] != B or v.shape[0] != B or v.shape[2] != N:
+            raise ValueError("batch / sequence sizes of q, k, v are inconsistent")
+
+        if sm_scale is None:
+            sm_scale = 1.0 / math.sqrt(D)
+        dropout_p = float(dropout_p)
+        is_dropout = dropout_p > 0
+
+        q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
+        lib = _lib.load()
+        device = q.device
+        with torch.cuda.device(device):
+            if is_dropout:
+                seed, offset = reserve_philox_stream(B * H * M * N, device)
+            else:
+                seed, offset = 0, 0
+            num_sms = torch.cuda.get_device_properties(device).multi_processor_count
+            num_splits = choose_num_splits(B, H, M, N, num_sms)
+            stream = _lib.current_stream_ptr(device)
+            status = _status_word(device)
+            L = torch.empty((B, H, M), device=device, dtype=torch.float32)
+            if num_splits > 1:
+                assert not is_dropout, "Cannot apply dropout with splitkv."
+                o = torch.empty_like(q)
+                o = o if _tma_ready(o) is o else torch.empty(q.shape, dtype=q.dtype, device=device)
+                part_o = torch.empty((B, H, num_splits, M, D), dtype=torch.float32, device=device)
+                part_l = torch.empty((B, H, num_splits, M), dtype=torch.float32, device=device)
+                sp = _lib.SplitKVParams(
+                    _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o),
+                    L.data_ptr(), part_o.data_ptr(), part_l.data_ptr(),
+                    B, H, Hk, M, N, D, num_splits, _lib.dtype_code(q.dtype), int(bool(causal)),
+                    float(sm_scale), status.data_ptr())
+                _lib.check(lib.b200attn_fwd_splitkv(sp, stream), "b200attn_fwd_splitkv")
+            else:
+                # Backward's row statistic is dot(O, dO): keep the fp32 O for bf16 dropout gradients,
+                # as the reference does (flash.py:86-90).
+                out_dtype = (torch.float32 if is_dropout and q.dtype == torch.bfloat16
+                             and any(ctx.needs_input_grad[:3]) else q.dtype)
+                o = torch.empty_like(q, dtype=out_dtype)
+                if _tma_ready(o) is not o:
+                    o = torch.empty(q.shape, dtype=out_dtype, device=device)
+                fp = _lib.FwdParams(
+                    _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), L.data_ptr(),
+                    B, H, Hk, M, N, D, _lib.dtype_code(q.dtype), _lib.dtype_code(out_dtype),
+                    int(bool(causal)), float(sm_scale), dropout_p, as_u64(seed), as_u64(offset),
+                    status.data_ptr())
+                _lib.check(lib.b200attn_fwd(fp, stream), "b200attn_fwd")
+
+            tot_attn = None
+            if return_total_attention:
+                tot_attn = torch.empty((B, H, N), device=device, dtype=torch.float32)
+                tp = _lib.TotalParams(
+                    _lib.tensor4(q), _lib.tensor4(k), L.data_ptr(), tot_attn.data_ptr(),
+                    B, H, Hk, M, N, D, _lib.dtype_code(q.dtype), int(bool(causal)), float(sm_scale),
+                    status.data_ptr())
+                _lib.check(lib.b200attn_total_attention(tp, stream), "b200attn_total_attention")
+
+        ctx.save_for_backward(q, k, v, o, L)
+        ctx.sm_scale = sm_scale
+        ctx.causal = bool(causal)
+        ctx.dropout_p = dropout_p
+        ctx.seed = seed
+        ctx.offset = offset
+        o = o.to(q.dtype)
+
+        if return_log_normalizer or return_total_attention or return_seed_offset:
+            return (
+                o,
+                L if return_log_normalizer else None,
+                tot_attn if return_total_attention else None,
+                seed if is_dropout and return_seed_offset else None,
+                offset if is_dropout and return_seed_offset else None,
+            )
+        return o
+
+    @staticmethod
+    def backward(ctx, do, *ignored):
+        q, k, v, o, L = ctx.saved_tensors
+        B, H, M, D = q.shape
+        N = k.shape[2]
+        Hk = k.shape[1]
+        device = q.device
+        if do.dtype != q.dtype:
+            do = do.to(q.dtype)
+        do = _vec_ready(do)
+        lib = _lib.load()
+        with torch.cuda.device(device):
+            stream = _lib.current_stream_ptr(device)
+            status = _status_word(device)
+            dq = torch.empty_like(q)
+            if _tma_ready(dq) is not dq:
+                dq = torch.empty(q.shape, dtype=q.dtype, device=device)
+            dk = torch.empty((B, Hk, N, D), dtype=k.dtype, device=device)
+            dv = torch.empty((B, Hk, N, D), dtype=v.dtype, device=device)
+            delta = torch.empty_like(L)
+            ws_bytes = lib.b200attn_bwd_workspace_bytes(B, H, Hk, M, N, D)
+            workspace = torch.zeros(max(ws_bytes, 4) // 4, dtype=torch.float32, device=device)
+            bp = _lib.BwdParams(
+                _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), _lib.tensor4(do),
+                _lib.tensor4(dq), _lib.tensor4(dk), _lib.tensor4(dv),
+                L.data_ptr(), delta.data_ptr(), workspace.data_ptr(),
+                B, H, Hk, M, N, D, _lib.dtype_code(q.dtype), _lib.dtype_code(o.dtype),
+                int(ctx.causal), float(ctx.sm_scale), float(ctx.dropout_p),
+                as_u64(ctx.seed), as_u64(ctx.offset), status.data_ptr())
+            _lib.check(lib.b200attn_bwd(bp, stream), "b200attn_bwd")
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def flash_attention(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
+                    return_log_normalizer=False, return_total_attention=False,
+                    return_seed_offset=False):
+    """FlashAttention forward (and, through autograd, backward) on B200.
+
+    Arguments:
+        q: ``(batch, heads_q, seqlen_q, headdim)`` fp16/bf16 CUDA tensor.
+        k, v: ``(batch, heads_k, seqlen_k, headdim)``; ``heads_q`` must be a multiple of ``heads_k``.
+        causal: bottom-right aligned causal mask (query ``m`` sees key ``n`` iff
+            ``n <= m + seqlen_k - seqlen_q``).
+        sm_scale: softmax scale, default ``1/sqrt(headdim)``.
+        dropout_p: dropout probability on the attention weights; the Philox stream is taken from
+            the default CUDA generator.
+        return_log_normalizer / return_total_attention / return_seed_offset: when any is set the
+            result is the 5-tuple ``(out, log_normalizer|None, total_attention|None, seed|None,
+            offset|None)``; otherwise just ``out``.
+    """
+    return FlashAttentionFunction.apply(q, k, v, causal, sm_scale, dropout_p, return_log_normalizer,
+                                        return_total_attention, return_seed_offset)

@@ -1,0 +1,164 @@
+/*
+ * C ABI of libb200attn: the sm_100a kernels behind flag_attn.flash_attention.
+ *
+ * Conventions
+ *  - Every pointer in a params struct is a DEVICE pointer owned by the caller; the
+ *    library allocates nothing, keeps no pointer after the call returns and only
+ *    enqueues work on `stream` (a cudaStream_t passed as void*).
+ *  - Tensors are addressed as [batch, head, row, feature] with four ELEMENT strides;
+ *    the feature stride must be 1 and the other three multiples of 8 elements
+ *    (16 bytes) with a 16-byte aligned base, because tiles are fetched by TMA.
+ *  - Every function returns 0 on success and a negative B200ATTN_E* code otherwise;
+ *    b200attn_last_error() then returns a thread-local message.
+ *  - `status` (optional, may be NULL) is a device int32 the kernels set to a non-zero
+ *    code when a bounded device-side wait gave up; it must be zero on entry.
+ */
+#ifndef B200ATTN_H_
+#define B200ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200ATTN_ABI_VERSION 1
+
+enum {
+  B200ATTN_OK = 0,
+  B200ATTN_EINVAL = -1,       /* bad shape / stride / dtype / pointer          */
+  B200ATTN_EUNSUPPORTED = -2, /* valid request the kernels do not implement    */
+  B200ATTN_ECUDA = -3,        /* a CUDA runtime / driver call failed           */
+  B200ATTN_ETIMEOUT = -4      /* device-side bounded wait expired (status word)*/
+};
+
+enum { B200ATTN_F16 = 0, B200ATTN_BF16 = 1, B200ATTN_F32 = 2 };
+
+typedef struct {
+  void* ptr;
+  int64_t stride[4]; /* elements: batch, head, row, feature */
+} b200attn_tensor;
+
+/* Forward: replaces the launch of `_fwd_kernel` (flash.py:92-105, kernel flash.py:345-509).
+ * o = softmax(q k^T * sm_scale [+causal mask]) [dropout] v ; lse = natural-log normaliser. */
+typedef struct {
+  b200attn_tensor q;   /* [B, Hq, M, D]  dtype                                   */
+  b200attn_tensor k;   /* [B, Hkv, N, D] dtype                                   */
+  b200attn_tensor v;   /* [B, Hkv, N, D] dtype                                   */
+  b200attn_tensor o;   /* [B, Hq, M, D]  o_dtype (dtype, or F32)                 */
+  float* lse;          /* [B, Hq, M] contiguous fp32                             */
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t dtype;       /* B200ATTN_F16 | B200ATTN_BF16                           */
+  int32_t o_dtype;     /* dtype or B200ATTN_F32                                  */
+  int32_t causal;      /* bottom-right aligned: key n visible iff n <= m + N - M */
+  float sm_scale;
+  float dropout_p;     /* 0 disables dropout                                     */
+  uint64_t seed;       /* Philox key                                             */
+  uint64_t offset;     /* Philox counter base                                    */
+  int32_t* status;     /* optional device status word                            */
+} b200attn_fwd_params;
+
+int b200attn_fwd(const b200attn_fwd_params* p, void* stream);
+
+/* Total attention: replaces `_total_attention_kernel` (total.py:64-156, launched
+ * flash.py:147-159). tot[b,h,n] = sum_m exp(s[m,n]*sm_scale - lse[m]) over visible m. */
+typedef struct {
+  b200attn_tensor q;
+  b200attn_tensor k;
+  const float* lse;    /* [B, Hq, M] */
+  float* tot;          /* [B, Hq, N] */
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t dtype;
+  int32_t causal;
+  float sm_scale;
+  int32_t* status;
+} b200attn_total_params;
+
+int b200attn_total_attention(const b200attn_total_params* p, void* stream);
+
+/* Backward: replaces `_bwd_preprocess`, `_bwd_kv_kernel`, `_bwd_q_kernel` and the GQA group
+ * sum (flash.py:183-272, kernels flash.py:542-931).
+ * Workspace: `delta` [B,Hq,M] fp32 and `dq_acc` (fp32, b200attn_bwd_workspace_bytes) are
+ * caller-allocated scratch; dq_acc must be zero on entry. */
+typedef struct {
+  b200attn_tensor q, k, v, o, d_o; /* o has o_dtype; d_o has dtype           */
+  b200attn_tensor dq;              /* [B, Hq, M, D]  dtype                   */
+  b200attn_tensor dk, dv;          /* [B, Hkv, N, D] dtype (group-summed)    */
+  const float* lse;                /* [B, Hq, M]                             */
+  float* delta;                    /* [B, Hq, M] scratch                     */
+  void* workspace;                 /* b200attn_bwd_workspace_bytes(), zeroed */
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t dtype, o_dtype;
+  int32_t causal;
+  float sm_scale;
+  float dropout_p;
+  uint64_t seed, offset;
+  int32_t* status;
+} b200attn_bwd_params;
+
+size_t b200attn_bwd_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t M, int32_t N,
+                                    int32_t D);
+int b200attn_bwd(const b200attn_bwd_params* p, void* stream);
+
+/* delta[b,h,m] = sum_d o*do in fp32: replaces `_bwd_preprocess` (flash.py:542-588). Also run
+ * inside b200attn_bwd; exported for tests. */
+int b200attn_bwd_delta(const b200attn_tensor* o, int32_t o_dtype, const b200attn_tensor* d_o,
+                       int32_t do_dtype, float* delta, int32_t B, int32_t H, int32_t M, int32_t D,
+                       void* stream);
+
+/* Dropout keep-mask materialisation: replaces the test helper `recompute_mask_kernel`
+ * (testing/dropout.py:19-39). mask[b,h,m,n] (uint8, contiguous) = 1 iff the element is kept. */
+int b200attn_dropout_mask(uint8_t* mask, int32_t B, int32_t H, int32_t M, int32_t N, float dropout_p,
+                          uint64_t seed, uint64_t offset, void* stream);
+
+/* Split-KV forward + combine: replaces `_fwd_split_kv_kernel` / `_fwd_combine_kv_splits`
+ * (split_kv.py:28-243, dispatched flash.py:106-144). part_o [B,Hq,S,M,D] fp32 and
+ * part_lse [B,Hq,S,M] fp32 are caller-allocated scratch. */
+typedef struct {
+  b200attn_tensor q, k, v, o;
+  float* lse;          /* [B, Hq, M] */
+  float* part_o;       /* [B, Hq, S, M, D] fp32 scratch */
+  float* part_lse;     /* [B, Hq, S, M] fp32 scratch    */
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t num_splits;  /* S >= 1 */
+  int32_t dtype;
+  int32_t causal;
+  float sm_scale;
+  int32_t* status;
+} b200attn_splitkv_params;
+
+int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stream);
+
+/* Diagnostics. */
+int b200attn_abi_version(void);
+const char* b200attn_last_error(void);
+
+/* One 128xN tcgen05 tile product with caller-chosen descriptor fields; used by the GPU
+ * tests to pin the shared-memory / TMEM operand layouts the attention kernels rely on.
+ * No counterpart in the reference. */
+typedef struct {
+  const void* a;       /* [128, a_cols] row-major 16-bit          */
+  const void* b;       /* [b_rows, b_cols] row-major 16-bit       */
+  float* d;            /* [128, n] fp32 out                       */
+  int32_t a_cols, b_rows, b_cols;
+  int32_t box_cols;    /* TMA box width in elements (<= 64)       */
+  int32_t swizzle;     /* 0 none, 1 32B, 2 64B, 3 128B (TMA enum) */
+  int32_t bf16;
+  int32_t a_in_tmem;   /* stage A through TMEM (packed 16-bit)    */
+  int32_t n;           /* MMA N                                   */
+  int32_t k_steps;     /* number of K=16 MMAs                     */
+  uint32_t idesc;
+  uint64_t a_desc_hi, b_desc_hi;   /* descriptor bits above the address   */
+  int32_t a_step_bytes, b_step_bytes; /* start-address advance per K step */
+  int32_t a_chunk_steps, b_chunk_steps; /* K steps per TMA chunk (0 = all in one) */
+  int32_t a_chunk_bytes, b_chunk_bytes; /* byte jump between chunks                */
+  int32_t* status;
+} b200attn_selftest_params;
+
+int b200attn_umma_selftest(const b200attn_selftest_params* p, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ATTN_H_ */
