@@ -1,0 +1,60 @@
+import json
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _exact_fp32_matmul():
+    # The fp32 oracle must not run on TF32 tensor cores (the reference's tests do the same,
+    # tests/conftest.py:8-16).
+    prev = torch.get_float32_matmul_precision()
+    torch.set_float32_matmul_precision("highest")
+    torch.backends.cuda.matmul.allow_tf32 = False
+    yield
+    torch.set_float32_matmul_precision(prev)
+
+
+def _from_bits(arr: np.ndarray, dtype: str) -> torch.Tensor:
+    if arr.dtype == np.uint16:
+        t = torch.from_numpy(arr.view(np.int16).copy())
+        return t.view(torch.float16 if dtype == "float16" else torch.bfloat16)
+    return torch.from_numpy(arr.copy())
+
+
+def load_golden(name: str) -> dict:
+    """Loads a fixture written by tests/golden/make_golden.py; 16-bit arrays come back as torch
+    tensors of the case's dtype, the dropout mask as a bool tensor (or None)."""
+    z = np.load(GOLDEN / f"{name}.npz")
+    meta = json.loads(str(z["meta"]))
+    out = {"meta": meta}
+    for key in z.files:
+        if key in ("meta", "mask"):
+            continue
+        out[key] = _from_bits(z[key], meta["dtype"])
+    if "mask" in z.files and z["mask"].size:
+        B, H, M, N = meta["B"], meta["Hq"], meta["M"], meta["N"]
+        out["mask"] = torch.from_numpy(np.unpackbits(z["mask"])[: B * H * M * N].reshape(B, H, M, N).astype(bool))
+    else:
+        out["mask"] = None
+    return out
+
+
+ATTENTION_GOLDENS = ["attention_c1_plumbing", "attention_gqa_causal_bf16", "attention_mqa_ragged_fp16",
+                     "attention_larger_m_causal", "attention_dropout_fp16", "attention_dropout_bf16_gqa"]
+TRITON_GOLDENS = ["triton_interp_causal0_p0", "triton_interp_causal0_p3", "triton_interp_causal1_p0",
+                  "triton_interp_causal1_p3"]

@@ -1,0 +1,66 @@
+"""CPU-only checks of the host side: library loading, exported symbols, argument validation,
+the split-KV dispatch rule and the wrapper's contract errors. No kernel is launched."""
+import ctypes
+import json
+import re
+
+import pytest
+import torch
+
+from conftest import GOLDEN, ROOT
+from flagattention_b200 import _lib, flash_attention
+from flagattention_b200.split_kv import choose_num_splits
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "b200attn.h").read_text()
+    declared = set(re.findall(r"\b(b200attn_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SYMBOLS), "ctypes table and header disagree"
+    lib = ctypes.CDLL(str(_lib.lib_path()))
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert _lib.load().b200attn_abi_version() == 1
+
+
+def test_invalid_arguments_are_rejected_before_any_cuda_call():
+    lib = _lib.load()
+    assert lib.b200attn_fwd(None, None) == -1
+    p = _lib.FwdParams()
+    p.B, p.Hq, p.Hkv, p.M, p.N, p.D = 1, 4, 3, 16, 16, 64
+    assert lib.b200attn_fwd(p, None) == -1
+    assert b"multiple" in lib.b200attn_last_error()
+    p.Hkv, p.D = 2, 48
+    assert lib.b200attn_fwd(p, None) == -1
+    assert b"head dimension" in lib.b200attn_last_error()
+    assert lib.b200attn_dropout_mask(None, 1, 1, 1, 1, 0.5, 0, 0, None) == -1
+    assert lib.b200attn_bwd(None, None) == -1
+    assert lib.b200attn_total_attention(None, None) == -1
+    assert lib.b200attn_fwd_splitkv(None, None) == -1
+
+
+def test_split_rule_matches_reference_table():
+    rows = json.loads((GOLDEN / "split_heuristic.json").read_text())
+    for B, H, M, N, sms, want in rows:
+        assert choose_num_splits(B, H, M, N, sms) == want, (B, H, M, N, sms)
+
+
+def test_baseline_configs_do_not_split():
+    for (B, H, M, N) in [(1, 4, 128, 128), (4, 32, 4096, 4096), (16, 16, 2048, 2048), (8, 16, 512, 8192),
+                         (1, 64, 32768, 32768)]:
+        assert choose_num_splits(B, H, M, N, 148) == 1
+
+
+def test_contract_violations_raise_like_the_reference():
+    q = torch.zeros(1, 4, 8, 64, dtype=torch.float16)
+    with pytest.raises(AssertionError, match="feature size"):
+        flash_attention(q, torch.zeros(1, 4, 8, 32, dtype=torch.float16), q)
+    with pytest.raises(AssertionError):
+        flash_attention(torch.zeros(1, 4, 8, 48), torch.zeros(1, 4, 8, 48), torch.zeros(1, 4, 8, 48))
+    with pytest.raises(AssertionError, match="k and v"):
+        flash_attention(q, torch.zeros(1, 2, 8, 64, dtype=torch.float16), q)
+    with pytest.raises(AssertionError, match="multiple"):
+        k = torch.zeros(1, 3, 8, 64, dtype=torch.float16)
+        flash_attention(q, k, k)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        flash_attention(q, q, q)  # CPU tensors: there is no CPU path
