@@ -38,7 +38,7 @@ class FwdParams(Structure):
 class TotalParams(Structure):
     _fields_ = [
         ("q", Tensor4), ("k", Tensor4),
-        ("lse", c_void_p), ("tot", c_void_p),
+        ("lse", c_void_p), ("tot", c_void_p), ("workspace", c_void_p),
         ("B", c_int32), ("Hq", c_int32), ("Hkv", c_int32), ("M", c_int32), ("N", c_int32), ("D", c_int32),
         ("dtype", c_int32), ("causal", c_int32), ("sm_scale", c_float),
         ("status", c_void_p),
@@ -85,6 +85,7 @@ class SelftestParams(Structure):
 # name -> (restype, argtypes); every symbol include/b200attn.h declares.
 SYMBOLS = {
     "b200attn_fwd": (c_int32, [POINTER(FwdParams), c_void_p]),
+    "b200attn_total_workspace_bytes": (c_size_t, [c_int32] * 3),
     "b200attn_total_attention": (c_int32, [POINTER(TotalParams), c_void_p]),
     "b200attn_bwd_workspace_bytes": (c_size_t, [c_int32] * 6),
     "b200attn_bwd": (c_int32, [POINTER(BwdParams), c_void_p]),

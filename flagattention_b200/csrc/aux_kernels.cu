@@ -80,6 +80,38 @@ delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __
   if (row_id < total && (lane % LANES) == 0) delta[row_id] = acc;
 }
 
+// stats[b, h, m] = (lse * log2(e), delta) for m < M and (+inf, 0) for the padding rows m in
+// [M, Mpad). Rows without any visible key (lse = -inf) also get +inf so that every probability
+// recomputed against them is exactly 0.
+__global__ void __launch_bounds__(256)
+stats_kernel(const float* __restrict__ lse, const float* __restrict__ delta, float2* __restrict__ stats,
+             int64_t BH, int M, int Mpad) {
+  const int64_t total = BH * Mpad;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t bh = i / Mpad;
+    const int m = static_cast<int>(i - bh * Mpad);
+    float2 out = make_float2(INFINITY, 0.f);
+    if (m < M) {
+      const float l = lse[bh * M + m];
+      out.x = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+      out.y = delta != nullptr ? delta[bh * M + m] : 0.f;
+    }
+    stats[i] = out;
+  }
+}
+
+int launch_stats(const float* lse, const float* delta, float2* stats, int B, int H, int M, int Mpad,
+                 cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(B) * H * Mpad;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  stats_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(lse, delta, stats,
+                                                                  static_cast<int64_t>(B) * H, M, Mpad);
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
+}
+
 template <int D>
 static int launch_delta(const b200attn_tensor* o, int o_dtype, const b200attn_tensor* d_o, int do_dtype,
                         float* delta, int B, int H, int M, cudaStream_t stream) {

@@ -1,0 +1,234 @@
+// C entry points of the backward pass and of total attention: validation, TMA descriptors,
+// the preprocess launches and the dispatch on head dimension.
+#include "bwd_launch.cuh"
+
+namespace b200attn {
+
+static int pad128(int m) { return (m + 127) / 128 * 128; }
+
+static int check_common(const char* who, int B, int Hq, int Hkv, int M, int N, int D, int dtype) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || M <= 0 || N <= 0) {
+    set_error("%s: B, Hq, Hkv, M, N must be positive", who);
+    return B200ATTN_EINVAL;
+  }
+  if (Hq % Hkv != 0) {
+    set_error("%s: number of heads in q must be a multiple of that in k & v", who);
+    return B200ATTN_EINVAL;
+  }
+  if (D != 16 && D != 32 && D != 64 && D != 128) {
+    set_error("%s: head dimension %d not in {16, 32, 64, 128}", who, D);
+    return B200ATTN_EINVAL;
+  }
+  if (dtype != B200ATTN_F16 && dtype != B200ATTN_BF16) {
+    set_error("%s: dtype must be fp16 or bf16", who);
+    return B200ATTN_EINVAL;
+  }
+  if (B > 65535 || Hq > 65535) {
+    set_error("%s: B and Hq are limited to 65535", who);
+    return B200ATTN_EINVAL;
+  }
+  return B200ATTN_OK;
+}
+
+static int check_out(const b200attn_tensor& t, const char* name) {
+  if (t.ptr == nullptr || t.stride[3] != 1 || reinterpret_cast<uintptr_t>(t.ptr) % 16 != 0 ||
+      (t.stride[0] * 2) % 16 != 0 || (t.stride[1] * 2) % 16 != 0 || (t.stride[2] * 2) % 16 != 0) {
+    set_error("%s: needs a non-null 16-byte aligned base, feature stride 1 and 16-byte strides", name);
+    return B200ATTN_EINVAL;
+  }
+  return B200ATTN_OK;
+}
+
+template <int D>
+static int encode_pair(CUtensorMap* m128, CUtensorMap* m64, const b200attn_tensor& t, int B, int H,
+                       int rows, const char* name) {
+  using Cfg = TileCfg<D>;
+  if (m128 != nullptr) {
+    int rc = encode_tmap_4d(m128, t, 2, B, H, rows, D, Cfg::CHUNK, 128, Cfg::TMA_SWZ, name);
+    if (rc) return rc;
+  }
+  if (m64 != nullptr) {
+    int rc = encode_tmap_4d(m64, t, 2, B, H, rows, D, Cfg::CHUNK, 64, Cfg::TMA_SWZ, name);
+    if (rc) return rc;
+  }
+  return B200ATTN_OK;
+}
+
+static int dispatch(int D, const BwdLaunch& L) {
+  switch (D) {
+    case 16: return launch_bwd_d16(L);
+    case 32: return launch_bwd_d32(L);
+    case 64: return launch_bwd_d64(L);
+    default: return launch_bwd_d128(L);
+  }
+}
+
+template <int D>
+static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t stream) {
+  BwdLaunch kv, qq;
+  int rc;
+  // MODE_KV: resident K, V (128-row boxes); streamed Q, dO (64-row boxes).
+  if ((rc = encode_pair<D>(&kv.tmA1, &qq.tmB1, p->k, p->B, p->Hkv, p->N, "k"))) return rc;
+  if ((rc = encode_pair<D>(&kv.tmA2, &qq.tmB2, p->v, p->B, p->Hkv, p->N, "v"))) return rc;
+  if ((rc = encode_pair<D>(&qq.tmA1, &kv.tmB1, p->q, p->B, p->Hq, p->M, "q"))) return rc;
+  if ((rc = encode_pair<D>(&qq.tmA2, &kv.tmB2, p->d_o, p->B, p->Hq, p->M, "do"))) return rc;
+
+  BwdArgs a{};
+  a.stats = stats;
+  a.tot = nullptr;
+  a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
+  a.Mpad = pad128(p->M);
+  a.groups = p->Hq / p->Hkv;
+  a.causal = p->causal ? 1 : 0;
+  a.sm_scale = p->sm_scale;
+  a.qk_scale = p->sm_scale * 1.4426950408889634f;
+  a.drop = make_dropout_ctx(p->dropout_p, p->seed, p->offset);
+  a.status = p->status;
+
+  kv.args = a;
+  kv.args.out1 = p->dk.ptr;
+  kv.args.out1_sb = p->dk.stride[0]; kv.args.out1_sh = p->dk.stride[1]; kv.args.out1_sr = p->dk.stride[2];
+  kv.args.out2 = p->dv.ptr;
+  kv.args.out2_sb = p->dv.stride[0]; kv.args.out2_sh = p->dv.stride[1]; kv.args.out2_sr = p->dv.stride[2];
+  kv.grid = dim3(static_cast<unsigned>(cdiv(p->N, 128)), static_cast<unsigned>(p->Hkv),
+                 static_cast<unsigned>(p->B));
+  kv.bf16 = p->dtype == B200ATTN_BF16;
+  kv.dropout = p->dropout_p > 0.f;
+  kv.mode = MODE_KV;
+  kv.stream = stream;
+
+  qq.args = a;
+  qq.args.out1 = p->dq.ptr;
+  qq.args.out1_sb = p->dq.stride[0]; qq.args.out1_sh = p->dq.stride[1]; qq.args.out1_sr = p->dq.stride[2];
+  qq.args.out2 = nullptr;
+  qq.grid = dim3(static_cast<unsigned>(cdiv(p->M, 128)), static_cast<unsigned>(p->Hq),
+                 static_cast<unsigned>(p->B));
+  qq.bf16 = kv.bf16;
+  qq.dropout = kv.dropout;
+  qq.mode = MODE_Q;
+  qq.stream = stream;
+
+  if ((rc = dispatch(D, kv))) return rc;
+  return dispatch(D, qq);
+}
+
+template <int D>
+static int run_total(const b200attn_total_params* p, float2* stats, cudaStream_t stream) {
+  BwdLaunch L;
+  int rc;
+  if ((rc = encode_pair<D>(&L.tmA1, nullptr, p->k, p->B, p->Hkv, p->N, "k"))) return rc;
+  if ((rc = encode_pair<D>(nullptr, &L.tmB1, p->q, p->B, p->Hq, p->M, "q"))) return rc;
+  L.tmA2 = L.tmA1;
+  L.tmB2 = L.tmB1;
+  BwdArgs a{};
+  a.stats = stats;
+  a.tot = p->tot;
+  a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
+  a.Mpad = pad128(p->M);
+  a.groups = p->Hq / p->Hkv;
+  a.causal = p->causal ? 1 : 0;
+  a.sm_scale = p->sm_scale;
+  a.qk_scale = p->sm_scale * 1.4426950408889634f;
+  a.drop = make_dropout_ctx(0.f, 0, 0);
+  a.status = p->status;
+  L.args = a;
+  L.grid = dim3(static_cast<unsigned>(cdiv(p->N, 128)), static_cast<unsigned>(p->Hq),
+                static_cast<unsigned>(p->B));
+  L.bf16 = p->dtype == B200ATTN_BF16;
+  L.dropout = false;
+  L.mode = MODE_TOTAL;
+  L.stream = stream;
+  return dispatch(D, L);
+}
+
+}  // namespace b200attn
+
+extern "C" size_t b200attn_bwd_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t M, int32_t N,
+                                               int32_t D) {
+  (void)Hkv; (void)N; (void)D;
+  if (B <= 0 || Hq <= 0 || M <= 0) return 0;
+  return static_cast<size_t>(B) * Hq * b200attn::pad128(M) * sizeof(float2);
+}
+
+extern "C" size_t b200attn_total_workspace_bytes(int32_t B, int32_t Hq, int32_t M) {
+  if (B <= 0 || Hq <= 0 || M <= 0) return 0;
+  return static_cast<size_t>(B) * Hq * b200attn::pad128(M) * sizeof(float2);
+}
+
+extern "C" int b200attn_bwd(const b200attn_bwd_params* p, void* stream_) {
+  using namespace b200attn;
+  if (p == nullptr) {
+    set_error("bwd: null params");
+    return B200ATTN_EINVAL;
+  }
+  int rc = check_common("bwd", p->B, p->Hq, p->Hkv, p->M, p->N, p->D, p->dtype);
+  if (rc) return rc;
+  if (p->o_dtype != p->dtype && p->o_dtype != B200ATTN_F32) {
+    set_error("bwd: o_dtype must equal dtype or be fp32");
+    return B200ATTN_EINVAL;
+  }
+  if (p->lse == nullptr || p->delta == nullptr || p->workspace == nullptr) {
+    set_error("bwd: lse, delta and workspace must be non-null");
+    return B200ATTN_EINVAL;
+  }
+  if (!(p->dropout_p >= 0.f && p->dropout_p < 1.f)) {
+    set_error("bwd: dropout_p must be in [0, 1)");
+    return B200ATTN_EINVAL;
+  }
+  if ((rc = check_out(p->dq, "bwd.dq"))) return rc;
+  if ((rc = check_out(p->dk, "bwd.dk"))) return rc;
+  if ((rc = check_out(p->dv, "bwd.dv"))) return rc;
+  if (reinterpret_cast<uintptr_t>(p->workspace) % 16 != 0) {
+    set_error("bwd: workspace must be 16-byte aligned");
+    return B200ATTN_EINVAL;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  rc = b200attn_bwd_delta(&p->o, p->o_dtype, &p->d_o, p->dtype, p->delta, p->B, p->Hq, p->M, p->D, stream_);
+  if (rc) return rc;
+  float2* stats = static_cast<float2*>(p->workspace);
+  rc = launch_stats(p->lse, p->delta, stats, p->B, p->Hq, p->M, pad128(p->M), stream);
+  if (rc) return rc;
+  switch (p->D) {
+    case 16: return run_bwd<16>(p, stats, stream);
+    case 32: return run_bwd<32>(p, stats, stream);
+    case 64: return run_bwd<64>(p, stats, stream);
+    default: return run_bwd<128>(p, stats, stream);
+  }
+}
+
+extern "C" int b200attn_total_attention(const b200attn_total_params* p, void* stream_) {
+  using namespace b200attn;
+  if (p == nullptr) {
+    set_error("total_attention: null params");
+    return B200ATTN_EINVAL;
+  }
+  int rc = check_common("total_attention", p->B, p->Hq, p->Hkv, p->M, p->N, p->D, p->dtype);
+  if (rc) return rc;
+  if (p->lse == nullptr || p->tot == nullptr || p->workspace == nullptr) {
+    set_error("total_attention: lse, tot and workspace must be non-null");
+    return B200ATTN_EINVAL;
+  }
+  if (reinterpret_cast<uintptr_t>(p->workspace) % 16 != 0) {
+    set_error("total_attention: workspace must be 16-byte aligned");
+    return B200ATTN_EINVAL;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  float2* stats = static_cast<float2*>(p->workspace);
+  rc = launch_stats(p->lse, nullptr, stats, p->B, p->Hq, p->M, pad128(p->M), stream);
+  if (rc) return rc;
+  switch (p->D) {
+    case 16: return run_total<16>(p, stats, stream);
+    case 32: return run_total<32>(p, stats, stream);
+    case 64: return run_total<64>(p, stats, stream);
+    default: return run_total<128>(p, stats, stream);
+  }
+}
+
+extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void*) {
+  if (p == nullptr) {
+    b200attn::set_error("fwd_splitkv: null params");
+    return B200ATTN_EINVAL;
+  }
+  b200attn::set_error("fwd_splitkv: not implemented");
+  return B200ATTN_EUNSUPPORTED;
+}

@@ -1,0 +1,451 @@
+// Backward / total-attention kernel family for sm_100a.
+//
+// One kernel template, three modes. In every mode a CTA owns 128 "row" indices whose tiles stay
+// resident in shared memory, and streams 64 "column" indices per step through a TMA ring:
+//
+//   MODE_KV    rows = keys n of one KV head, columns = queries m of every query head of its group.
+//              T1 = K Q^T, T2 = V dO^T (so probabilities come out transposed, key on the TMEM
+//              lane), dV += P^T dO, dK += dS^T Q. The group sum of dK/dV happens in the fp32
+//              accumulators. Replaces `_bwd_kv_kernel` (flash.py:591-765) + the sum at :270-271.
+//   MODE_Q     rows = queries m of one query head, columns = keys n.
+//              T1 = Q K^T, T2 = dO V^T, dQ += dS K. Replaces `_bwd_q_kernel` (flash.py:768-931).
+//   MODE_TOTAL rows = keys n of one query head's KV head, columns = queries m.
+//              T1 = K Q^T, tot[n] = sum_m P. Replaces `_total_attention_kernel` (total.py:64-156).
+//
+// P is recomputed as exp2(T1*qk_scale - lse*log2e) and dS = P * (dP - delta), with dropout applied
+// as in the reference (dV uses the masked P and is scaled by 1/(1-p) at the end; dP is masked and
+// scaled by 1/(1-p) before delta is subtracted).
+//
+// Roles: warps 0-3 and 4-7 are two softmax groups that alternate steps (thread r <-> row r), warp 8
+// issues tcgen05.mma, warp 9 drives TMA. TMEM: accumulators (D columns each) followed by two
+// (T1, T2) buffers of 64+64 fp32 columns; P / dS overwrite the head of T1 / T2 as packed 16-bit
+// pairs and are consumed from TMEM as the A operand of the accumulating MMAs.
+//
+// Per-column statistics come from a padded scratch array stats[b, h, m] = (lse*log2e, delta),
+// padded to a multiple of 128 queries with (+inf, 0) so that padded and key-less queries contribute
+// exactly zero.
+#pragma once
+#include "common.cuh"
+#include "fwd_kernel.cuh"
+#include "ptx.cuh"
+
+namespace b200attn {
+
+enum BwdMode : int { MODE_KV = 0, MODE_Q = 1, MODE_TOTAL = 2 };
+
+struct BwdArgs {
+  void* out1;  // MODE_KV: dK, MODE_Q: dQ
+  void* out2;  // MODE_KV: dV
+  int64_t out1_sb, out1_sh, out1_sr;
+  int64_t out2_sb, out2_sh, out2_sr;
+  const float2* stats;  // [B, Hq, Mpad] (lse*log2e, delta)
+  float* tot;           // MODE_TOTAL: [B, Hq, N]
+  int B, Hq, Hkv, M, N, Mpad, groups, causal;
+  float sm_scale, qk_scale;
+  DropoutCtx drop;
+  int32_t* status;
+};
+
+template <int D, int MODE>
+struct BwdSmem {
+  static constexpr int STAGES = 4;
+  static constexpr int N_A = MODE == MODE_TOTAL ? 1 : 2;       // resident tiles
+  static constexpr int N_B = MODE == MODE_TOTAL ? 1 : 2;       // streamed tiles per stage
+  static constexpr int A_BYTES = N_A * TileCfg<D>::TILE_BYTES; // 128 x D each
+  static constexpr int B_TILE_BYTES = 64 * D * 2;
+  static constexpr int STATS_BYTES = MODE == MODE_Q ? 0 : 512; // 64 x float2
+  static constexpr int STAGE_BYTES = N_B * B_TILE_BYTES + 1024; // tiles + stats slot (keeps 1 KB alignment)
+  static constexpr int BAR_OFFSET = A_BYTES + STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;
+};
+
+template <int D, bool BF16, bool DROPOUT, int MODE>
+__global__ void __launch_bounds__(320, 1)
+bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
+           const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
+           const BwdArgs args) {
+  using Cfg = TileCfg<D>;
+  using Sm = BwdSmem<D, MODE>;
+  constexpr int STAGES = Sm::STAGES;
+  constexpr int STEP = 64;                                  // columns per step
+  constexpr int CHUNK_BYTES_B = STEP * Cfg::ROW_BYTES;      // one [64 x CHUNK] box
+  constexpr uint64_t MN_DESC_B = make_smem_desc_hi(CHUNK_BYTES_B, 8 * Cfg::ROW_BYTES, Cfg::UMMA_SWZ);
+  constexpr int N_ACC = MODE == MODE_KV ? 2 : (MODE == MODE_Q ? 1 : 0);
+  constexpr uint32_t BUF_BASE = N_ACC * D;                  // TMEM column of buffer 0
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + Sm::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Sm::BAR_OFFSET);
+  uint64_t* a_full = bars;                 // [1]
+  uint64_t* b_full = bars + 1;             // [STAGES]
+  uint64_t* b_empty = b_full + STAGES;     // [STAGES]
+  uint64_t* t_full = b_empty + STAGES;     // [2]
+  uint64_t* p_ready = t_full + 2;          // [2]
+  uint64_t* acc_full = p_ready + 2;        // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int b = blockIdx.z;
+  const int P_SEQ = args.N - args.M;
+
+  // Row block, the heads it loops over and its column range [col_lo, col_hi) in steps of 64.
+  int r0, h_first, n_heads, hk, col_lo, col_hi;
+  if constexpr (MODE == MODE_Q) {
+    r0 = (gridDim.x - 1 - blockIdx.x) * 128;  // longest (causal) blocks first
+    h_first = blockIdx.y;
+    n_heads = 1;
+    hk = h_first / args.groups;
+    col_lo = 0;
+    col_hi = args.causal ? min(args.N, max(0, P_SEQ + r0 + 128)) : args.N;
+  } else {
+    r0 = blockIdx.x * 128;                    // small n0 = most visible queries = longest first
+    if constexpr (MODE == MODE_KV) {
+      hk = blockIdx.y;
+      h_first = hk * args.groups;
+      n_heads = args.groups;
+    } else {
+      h_first = blockIdx.y;
+      n_heads = 1;
+      hk = h_first / args.groups;
+    }
+    col_lo = args.causal ? (max(0, r0 - P_SEQ) / STEP) * STEP : 0;
+    col_hi = args.M;
+  }
+  const int steps_per_head = col_hi > col_lo ? cdiv(col_hi - col_lo, STEP) : 0;
+  const int T = steps_per_head * n_heads;
+
+  if (threadIdx.x == 0) {
+    mbar_init(a_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&b_full[s], 1);
+      mbar_init(&b_empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&t_full[i], 1);
+      mbar_init(&p_ready[i], 128);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&](int32_t code) {
+    report_status(args.status, code);
+    *abort_flag = 1;
+  };
+  auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((++spins & 0xffu) == 0u) {
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+      }
+    }
+  };
+
+  if (warp == 9) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && T > 0) {
+      tma_prefetch_desc(&tmA1);
+      tma_prefetch_desc(&tmB1);
+      if constexpr (MODE != MODE_TOTAL) {
+        tma_prefetch_desc(&tmA2);
+        tma_prefetch_desc(&tmB2);
+      }
+      const int a_head = MODE == MODE_Q ? h_first : hk;
+      mbar_expect_tx(a_full, Sm::A_BYTES);
+      for (int c = 0; c < Cfg::NCHUNK; ++c) {
+        tma_load_4d(sA + c * Cfg::CHUNK_BYTES, &tmA1, a_full, c * Cfg::CHUNK, r0, a_head, b);
+        if constexpr (MODE != MODE_TOTAL)
+          tma_load_4d(sA + Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmA2, a_full, c * Cfg::CHUNK, r0,
+                      a_head, b);
+      }
+      for (int i = 0; i < T; ++i) {
+        const int st = i % STAGES;
+        const int hh = i / steps_per_head;
+        const int col = col_lo + (i - hh * steps_per_head) * STEP;
+        const int b_head = MODE == MODE_Q ? hk : h_first + hh;
+        if (!wait(&b_empty[st], ((i / STAGES) & 1) ^ 1)) { fail(ST_WAIT_EMPTY); break; }
+        uint8_t* stage = sB + st * Sm::STAGE_BYTES;
+        mbar_expect_tx(&b_full[st], Sm::N_B * Sm::B_TILE_BYTES + Sm::STATS_BYTES);
+        for (int c = 0; c < Cfg::NCHUNK; ++c) {
+          tma_load_4d(stage + c * CHUNK_BYTES_B, &tmB1, &b_full[st], c * Cfg::CHUNK, col, b_head, b);
+          if constexpr (MODE != MODE_TOTAL)
+            tma_load_4d(stage + Sm::B_TILE_BYTES + c * CHUNK_BYTES_B, &tmB2, &b_full[st],
+                        c * Cfg::CHUNK, col, b_head, b);
+        }
+        if constexpr (MODE != MODE_Q) {
+          const float2* src = args.stats + (static_cast<int64_t>(b) * args.Hq + b_head) * args.Mpad + col;
+          asm volatile(
+              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+              ::"r"(smem_u32(stage + Sm::N_B * Sm::B_TILE_BYTES)),
+              "l"(reinterpret_cast<uint64_t>(src)), "r"(512), "r"(smem_u32(&b_full[st]))
+              : "memory");
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 8) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0 && T > 0) {
+      constexpr uint32_t IDESC_T = make_idesc(BF16, 128, STEP, false, false);
+      constexpr uint32_t IDESC_ACC = make_idesc(BF16, 128, D, false, true);
+      const uint32_t a_addr = smem_u32(sA);
+      const uint32_t b_addr = smem_u32(sB);
+      // T1 = A1 B1^T, T2 = A2 B2^T into buffer `buf` from ring stage `st`.
+      auto issue_t = [&](int buf, int st) {
+        const uint32_t t1 = tmem_base + BUF_BASE + buf * 128;
+        const uint32_t sb = b_addr + st * Sm::STAGE_BYTES;
+#pragma unroll
+        for (int which = 0; which < Sm::N_A; ++which) {
+#pragma unroll
+          for (int s = 0; s < D / 16; ++s) {
+            const uint32_t a_off = which * Cfg::TILE_BYTES + (s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
+                                   (s % Cfg::STEPS_PER_CHUNK) * 32;
+            const uint32_t b_off = which * Sm::B_TILE_BYTES + (s / Cfg::STEPS_PER_CHUNK) * CHUNK_BYTES_B +
+                                   (s % Cfg::STEPS_PER_CHUNK) * 32;
+            mma_ss(t1 + which * 64, smem_desc(Cfg::KMAJOR_DESC, a_addr + a_off),
+                   smem_desc(Cfg::KMAJOR_DESC, sb + b_off), IDESC_T, s > 0 ? 1u : 0u);
+          }
+        }
+      };
+      // acc[which] += (P or dS from TMEM) x streamed tile `tile` of stage `st`, read MN-major.
+      auto issue_acc = [&](int acc, int buf, int src, int st, int tile, bool accumulate) {
+        const uint32_t d = tmem_base + acc * D;
+        const uint32_t a = tmem_base + BUF_BASE + buf * 128 + src * 64;
+        const uint32_t sb = b_addr + st * Sm::STAGE_BYTES + tile * Sm::B_TILE_BYTES;
+#pragma unroll
+        for (int s = 0; s < STEP / 16; ++s)
+          mma_ts(d, a + s * 8, smem_desc(MN_DESC_B, sb + s * 16 * Cfg::ROW_BYTES), IDESC_ACC,
+                 (accumulate || s > 0) ? 1u : 0u);
+      };
+      bool ok = true;
+      if (!wait(a_full, 0)) { fail(ST_WAIT_TMA); ok = false; }
+      if (ok && !wait(&b_full[0], 0)) { fail(ST_WAIT_TMA); ok = false; }
+      if (ok) {
+        tc_fence_after();
+        issue_t(0, 0);
+        tc_commit(&t_full[0]);
+      }
+      for (int i = 0; i < T && ok; ++i) {
+        const int buf = i & 1;
+        const int st = i % STAGES;
+        if (i + 1 < T) {
+          const int st_next = (i + 1) % STAGES;
+          if (!wait(&b_full[st_next], ((i + 1) / STAGES) & 1)) { fail(ST_WAIT_TMA); ok = false; break; }
+          tc_fence_after();
+          issue_t(buf ^ 1, st_next);
+          tc_commit(&t_full[buf ^ 1]);
+        }
+        if (!wait(&p_ready[buf], (i >> 1) & 1)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+        tc_fence_after();
+        if constexpr (MODE == MODE_KV) {
+          issue_acc(1, buf, 0, st, 1, i > 0);  // dV += P^T  dO
+          issue_acc(0, buf, 1, st, 0, i > 0);  // dK += dS^T Q
+        } else if constexpr (MODE == MODE_Q) {
+          issue_acc(0, buf, 1, st, 0, i > 0);  // dQ += dS K
+        }
+        tc_commit(&b_empty[st]);
+      }
+      if (ok) tc_commit(acc_full);
+    }
+    __syncwarp();
+  } else {
+    // --------------------------------------------------------- softmax groups
+    const int wg = warp >> 2;
+    const int row_local = (warp & 3) * 32 + lane;
+    const int row = r0 + row_local;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const float qk_scale = args.qk_scale;
+    float row_lse2 = 0.f, row_delta = 0.f;
+    if constexpr (MODE == MODE_Q) {
+      if (row < args.Mpad) {
+        const float2 st = args.stats[(static_cast<int64_t>(b) * args.Hq + h_first) * args.Mpad + row];
+        row_lse2 = st.x;
+        row_delta = st.y;
+      } else {
+        row_lse2 = INFINITY;
+      }
+    }
+    float tot_sum = 0.f;
+    bool ok = true;
+
+    for (int i = wg; i < T; i += 2) {
+      const int st = i % STAGES;
+      const int hh = i / steps_per_head;
+      const int col0 = col_lo + (i - hh * steps_per_head) * STEP;
+      const int h = h_first + hh;
+      const uint32_t t1_addr = tmem_base + lane_base + BUF_BASE + wg * 128;
+      {
+        const bool w = wait(&t_full[wg], (i >> 1) & 1);
+        if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
+      }
+      tc_fence_after();
+      uint32_t t1[64];
+      uint32_t t2[MODE == MODE_TOTAL ? 1 : 64];
+      tmem_ld32(t1_addr, t1);
+      tmem_ld32(t1_addr + 32, t1 + 32);
+      if constexpr (MODE != MODE_TOTAL) {
+        tmem_ld32(t1_addr + 64, t2);
+        tmem_ld32(t1_addr + 96, t2 + 32);
+      }
+      tmem_wait_ld();
+
+      // Does this step cross the causal boundary for some row of the block?
+      bool diag = false;
+      if (args.causal) {
+        if constexpr (MODE == MODE_Q) diag = col0 + STEP - 1 > r0 + P_SEQ;
+        else diag = col0 + P_SEQ < r0 + 127;
+      }
+      const float4* stats4 = reinterpret_cast<const float4*>(sB + st * Sm::STAGE_BYTES + Sm::N_B * Sm::B_TILE_BYTES);
+      uint64_t ctr0 = 0, ctr_step = 0;
+      if constexpr (DROPOUT) {
+        const uint64_t head_base = args.drop.offset +
+                                   (static_cast<uint64_t>(b) * args.Hq + h) * args.M * static_cast<uint64_t>(args.N);
+        if constexpr (MODE == MODE_Q) {
+          ctr0 = head_base + static_cast<uint64_t>(row) * args.N + col0;
+          ctr_step = 1;
+        } else {
+          ctr0 = head_base + static_cast<uint64_t>(col0) * args.N + row;
+          ctr_step = args.N;
+        }
+      }
+
+#pragma unroll
+      for (int c = 0; c < STEP; c += 2) {
+        float lse_a, lse_b, del_a, del_b;
+        if constexpr (MODE == MODE_Q) {
+          lse_a = lse_b = row_lse2;
+          del_a = del_b = row_delta;
+        } else {
+          const float4 sv = stats4[c >> 1];
+          lse_a = sv.x; del_a = sv.y; lse_b = sv.z; del_b = sv.w;
+        }
+        float p_a = fast_exp2(fmaf(__uint_as_float(t1[c]), qk_scale, -lse_a));
+        float p_b = fast_exp2(fmaf(__uint_as_float(t1[c + 1]), qk_scale, -lse_b));
+        if (diag) {
+          bool vis_a, vis_b;
+          if constexpr (MODE == MODE_Q) {
+            vis_a = col0 + c <= row + P_SEQ;
+            vis_b = col0 + c + 1 <= row + P_SEQ;
+          } else {
+            vis_a = col0 + c + P_SEQ >= row;
+            vis_b = col0 + c + 1 + P_SEQ >= row;
+          }
+          p_a = vis_a ? p_a : 0.f;
+          p_b = vis_b ? p_b : 0.f;
+        }
+        if constexpr (MODE == MODE_TOTAL) {
+          tot_sum += p_a + p_b;
+        } else {
+          float dp_a = __uint_as_float(t2[c]);
+          float dp_b = __uint_as_float(t2[c + 1]);
+          float pd_a = p_a, pd_b = p_b;
+          if constexpr (DROPOUT) {
+            const bool keep_a = dropout_keep(args.drop, ctr0 + ctr_step * c);
+            const bool keep_b = dropout_keep(args.drop, ctr0 + ctr_step * (c + 1));
+            pd_a = keep_a ? p_a : 0.f;
+            pd_b = keep_b ? p_b : 0.f;
+            dp_a = keep_a ? dp_a * args.drop.inv_keep : 0.f;
+            dp_b = keep_b ? dp_b * args.drop.inv_keep : 0.f;
+          }
+          const float ds_a = p_a * (dp_a - del_a);
+          const float ds_b = p_b * (dp_b - del_b);
+          t1[c >> 1] = pack2<BF16>(pd_a, pd_b);
+          t2[c >> 1] = pack2<BF16>(ds_a, ds_b);
+        }
+      }
+      if constexpr (MODE != MODE_TOTAL) {
+        if constexpr (MODE == MODE_KV) tmem_st32(t1_addr, t1);
+        tmem_st32(t1_addr + 64, t2);
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      mbar_arrive(&p_ready[wg]);
+    }
+
+    // ------------------------------------------------------------- epilogue
+    if (ok && T > 0) {
+      const bool w = wait(acc_full, 0);
+      if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; }
+    }
+    if constexpr (MODE == MODE_TOTAL) {
+      // The two groups hold partial sums of alternating steps: combine through shared memory.
+      float* red = reinterpret_cast<float*>(sA);  // the resident tile is dead after acc_full
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (wg == 1) red[row_local] = tot_sum;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (wg == 0 && ok && row < args.N)
+        args.tot[(static_cast<int64_t>(b) * args.Hq + h_first) * args.N + row] = tot_sum + red[row_local];
+    } else if (ok) {
+      tc_fence_after();
+      const int n_rows = MODE == MODE_Q ? args.M : args.N;
+      const bool valid = row < n_rows;
+      const int out_head = MODE == MODE_Q ? h_first : hk;
+      // Group `wg` converts half of the columns of every accumulator.
+#pragma unroll
+      for (int acc = 0; acc < N_ACC; ++acc) {
+        void* out = acc == 0 ? args.out1 : args.out2;
+        const int64_t off = acc == 0
+                                ? b * args.out1_sb + out_head * args.out1_sh + static_cast<int64_t>(row) * args.out1_sr
+                                : b * args.out2_sb + out_head * args.out2_sh + static_cast<int64_t>(row) * args.out2_sr;
+        float scale = args.sm_scale;
+        if (MODE == MODE_KV && acc == 1) scale = DROPOUT ? args.drop.inv_keep : 1.0f;
+#pragma unroll
+        for (int c = wg * (D / 2); c < (wg + 1) * (D / 2); c += 8) {
+          uint32_t o[8];
+          __syncwarp();
+          if (T > 0) {
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]),
+                  "=r"(o[7])
+                : "r"(tmem_base + lane_base + acc * D + c)
+                : "memory");
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = 0u;
+          }
+          if (valid) {
+            uint4 v;
+            v.x = pack2<BF16>(__uint_as_float(o[0]) * scale, __uint_as_float(o[1]) * scale);
+            v.y = pack2<BF16>(__uint_as_float(o[2]) * scale, __uint_as_float(o[3]) * scale);
+            v.z = pack2<BF16>(__uint_as_float(o[4]) * scale, __uint_as_float(o[5]) * scale);
+            v.w = pack2<BF16>(__uint_as_float(o[6]) * scale, __uint_as_float(o[7]) * scale);
+            *reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + off + c) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  if (warp == 8) {
+    if (*abort_flag) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) {}
+    }
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace b200attn

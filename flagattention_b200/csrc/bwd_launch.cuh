@@ -1,0 +1,52 @@
+// Host launchers of the backward / total-attention kernel family; bwd_d*.cu instantiate one head
+// dimension each so the variants compile in parallel.
+#pragma once
+#include "bwd_kernel.cuh"
+
+namespace b200attn {
+
+struct BwdLaunch {
+  CUtensorMap tmA1, tmA2, tmB1, tmB2;
+  BwdArgs args;
+  dim3 grid;
+  bool bf16, dropout;
+  int mode;
+  cudaStream_t stream;
+};
+
+template <int D, bool BF16, bool DROPOUT, int MODE>
+int launch_bwd_variant(const BwdLaunch& L) {
+  auto kernel = bwd_kernel<D, BF16, DROPOUT, MODE>;
+  constexpr int smem = BwdSmem<D, MODE>::TOTAL;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  B200ATTN_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+    B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (dev >= 0 && dev < 64) attr_done[dev] = true;
+  }
+  kernel<<<L.grid, 320, smem, L.stream>>>(L.tmA1, L.tmA2, L.tmB1, L.tmB2, L.args);
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
+}
+
+template <int D>
+int launch_bwd_d(const BwdLaunch& L) {
+  if (L.mode == MODE_TOTAL) {
+    return L.bf16 ? launch_bwd_variant<D, true, false, MODE_TOTAL>(L)
+                  : launch_bwd_variant<D, false, false, MODE_TOTAL>(L);
+  }
+  if (L.mode == MODE_KV) {
+    if (L.bf16) return L.dropout ? launch_bwd_variant<D, true, true, MODE_KV>(L) : launch_bwd_variant<D, true, false, MODE_KV>(L);
+    return L.dropout ? launch_bwd_variant<D, false, true, MODE_KV>(L) : launch_bwd_variant<D, false, false, MODE_KV>(L);
+  }
+  if (L.bf16) return L.dropout ? launch_bwd_variant<D, true, true, MODE_Q>(L) : launch_bwd_variant<D, true, false, MODE_Q>(L);
+  return L.dropout ? launch_bwd_variant<D, false, true, MODE_Q>(L) : launch_bwd_variant<D, false, false, MODE_Q>(L);
+}
+
+int launch_bwd_d16(const BwdLaunch& L);
+int launch_bwd_d32(const BwdLaunch& L);
+int launch_bwd_d64(const BwdLaunch& L);
+int launch_bwd_d128(const BwdLaunch& L);
+
+}  // namespace b200attn

@@ -32,6 +32,11 @@ int encode_tmap_4d(CUtensorMap* out, const b200attn_tensor& t, int elem_bytes, i
 // Checks the TMA requirements of one operand; returns 0 or B200ATTN_EINVAL.
 int check_tma_operand(const b200attn_tensor& t, int elem_bytes, const char* name);
 
+// Writes the padded per-query statistics the backward / total-attention kernels stream
+// (aux_kernels.cu). `delta` may be null (total attention).
+int launch_stats(const float* lse, const float* delta, float2* stats, int B, int H, int M, int Mpad,
+                 cudaStream_t stream);
+
 // Smallest integer threshold T such that a Philox word x (folded to [0, 2^31)) is KEPT iff x > T,
 // equivalent to `float(x) * 4.6566127342e-10f > dropout_p` evaluated in fp32.
 int32_t dropout_keep_threshold(float dropout_p);

@@ -130,8 +130,10 @@ class FlashAttentionFunction(torch.autograd.Function):
             tot_attn = None
             if return_total_attention:
                 tot_attn = torch.empty((B, H, N), device=device, dtype=torch.float32)
+                ws = torch.empty(lib.b200attn_total_workspace_bytes(B, H, M) // 4, dtype=torch.float32,
+                                 device=device)
                 tp = _lib.TotalParams(
-                    _lib.tensor4(q), _lib.tensor4(k), L.data_ptr(), tot_attn.data_ptr(),
+                    _lib.tensor4(q), _lib.tensor4(k), L.data_ptr(), tot_attn.data_ptr(), ws.data_ptr(),
                     B, H, Hk, M, N, D, _lib.dtype_code(q.dtype), int(bool(causal)), float(sm_scale),
                     status.data_ptr())
                 _lib.check(lib.b200attn_total_attention(tp, stream), "b200attn_total_attention")
@@ -175,7 +177,7 @@ class FlashAttentionFunction(torch.autograd.Function):
             dv = torch.empty((B, Hk, N, D), dtype=v.dtype, device=device)
             delta = torch.empty_like(L)
             ws_bytes = lib.b200attn_bwd_workspace_bytes(B, H, Hk, M, N, D)
-            workspace = torch.zeros(max(ws_bytes, 4) // 4, dtype=torch.float32, device=device)
+            workspace = torch.empty(max(ws_bytes, 4) // 4, dtype=torch.float32, device=device)
             bp = _lib.BwdParams(
                 _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), _lib.tensor4(do),
                 _lib.tensor4(dq), _lib.tensor4(dk), _lib.tensor4(dv),

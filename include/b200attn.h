@@ -62,12 +62,15 @@ typedef struct {
 int b200attn_fwd(const b200attn_fwd_params* p, void* stream);
 
 /* Total attention: replaces `_total_attention_kernel` (total.py:64-156, launched
- * flash.py:147-159). tot[b,h,n] = sum_m exp(s[m,n]*sm_scale - lse[m]) over visible m. */
+ * flash.py:147-159). tot[b,h,n] = sum_m exp(s[m,n]*sm_scale - lse[m]) over visible m.
+ * `workspace` is caller-allocated scratch of b200attn_total_workspace_bytes(B, Hq, M) bytes,
+ * 16-byte aligned; its contents on entry do not matter. */
 typedef struct {
   b200attn_tensor q;
   b200attn_tensor k;
   const float* lse;    /* [B, Hq, M] */
   float* tot;          /* [B, Hq, N] */
+  void* workspace;
   int32_t B, Hq, Hkv, M, N, D;
   int32_t dtype;
   int32_t causal;
@@ -75,19 +78,21 @@ typedef struct {
   int32_t* status;
 } b200attn_total_params;
 
+size_t b200attn_total_workspace_bytes(int32_t B, int32_t Hq, int32_t M);
 int b200attn_total_attention(const b200attn_total_params* p, void* stream);
 
 /* Backward: replaces `_bwd_preprocess`, `_bwd_kv_kernel`, `_bwd_q_kernel` and the GQA group
  * sum (flash.py:183-272, kernels flash.py:542-931).
- * Workspace: `delta` [B,Hq,M] fp32 and `dq_acc` (fp32, b200attn_bwd_workspace_bytes) are
- * caller-allocated scratch; dq_acc must be zero on entry. */
+ * `delta` [B,Hq,M] fp32 and `workspace` (b200attn_bwd_workspace_bytes() bytes, 16-byte aligned)
+ * are caller-allocated scratch; their contents on entry do not matter. dK / dV are written
+ * already summed over each KV head's query group (accumulated in fp32). */
 typedef struct {
   b200attn_tensor q, k, v, o, d_o; /* o has o_dtype; d_o has dtype           */
   b200attn_tensor dq;              /* [B, Hq, M, D]  dtype                   */
   b200attn_tensor dk, dv;          /* [B, Hkv, N, D] dtype (group-summed)    */
   const float* lse;                /* [B, Hq, M]                             */
   float* delta;                    /* [B, Hq, M] scratch                     */
-  void* workspace;                 /* b200attn_bwd_workspace_bytes(), zeroed */
+  void* workspace;                 /* b200attn_bwd_workspace_bytes() scratch  */
   int32_t B, Hq, Hkv, M, N, D;
   int32_t dtype, o_dtype;
   int32_t causal;
