@@ -224,11 +224,3 @@ extern "C" int b200attn_total_attention(const b200attn_total_params* p, void* st
   }
 }
 
-extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void*) {
-  if (p == nullptr) {
-    b200attn::set_error("fwd_splitkv: null params");
-    return B200ATTN_EINVAL;
-  }
-  b200attn::set_error("fwd_splitkv: not implemented");
-  return B200ATTN_EUNSUPPORTED;
-}

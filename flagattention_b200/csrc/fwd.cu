@@ -78,6 +78,12 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
   a.o_stride_b = p->o.stride[0];
   a.o_stride_h = p->o.stride[1];
   a.o_stride_m = p->o.stride[2];
+  a.o_stride_split = 0;
+  a.lse_stride_b = static_cast<int64_t>(p->Hq) * p->M;
+  a.lse_stride_h = p->M;
+  a.lse_stride_split = 0;
+  a.num_splits = 1;
+  a.tiles_per_split = cdiv(p->N, 128);
   a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
   a.groups = p->Hq / p->Hkv;
   a.causal = p->causal ? 1 : 0;
@@ -97,4 +103,140 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
     case 64: return launch_fwd_d64(L);
     default: return launch_fwd_d128(L);
   }
+}
+
+// ------------------------------------------------------------------ split-KV
+namespace b200attn {
+
+// O[row] = sum_s w_s O_s[row] / sum_s w_s with w_s = exp(lse_s - max_s lse_s);
+// LSE[row] = max + log(sum_s w_s). One block per (b, h, m) row, one thread per feature.
+template <bool BF16>
+__global__ void splitkv_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                       void* __restrict__ o, float* __restrict__ lse, int64_t o_sb,
+                                       int64_t o_sh, int64_t o_sm, int H, int M, int D, int S) {
+  const int64_t row = blockIdx.x;  // (b*H + h)*M + m
+  const int m = static_cast<int>(row % M);
+  const int64_t bh = row / M;
+  const int h = static_cast<int>(bh % H);
+  const int64_t b = bh / H;
+  const float* l = part_lse + bh * S * M + m;
+  float mx = -INFINITY;
+  for (int s = 0; s < S; ++s) mx = fmaxf(mx, l[static_cast<int64_t>(s) * M]);
+  float denom = 0.f;
+  for (int s = 0; s < S; ++s) denom += (mx == -INFINITY) ? 0.f : expf(l[static_cast<int64_t>(s) * M] - mx);
+  const int d = threadIdx.x;
+  if (d < D) {
+    float acc = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float w = (mx == -INFINITY) ? 0.f : expf(l[static_cast<int64_t>(s) * M] - mx);
+      acc += w * part_o[((bh * S + s) * M + m) * D + d];
+    }
+    const float out = denom > 0.f ? acc / denom : 0.f;
+    uint16_t* dst = static_cast<uint16_t*>(o) + b * o_sb + h * o_sh + m * o_sm + d;
+    if constexpr (BF16) {
+      __nv_bfloat16 v = __float2bfloat16_rn(out);
+      *dst = *reinterpret_cast<uint16_t*>(&v);
+    } else {
+      __half v = __float2half_rn(out);
+      *dst = *reinterpret_cast<uint16_t*>(&v);
+    }
+  }
+  if (threadIdx.x == 0) lse[row] = denom > 0.f ? mx + logf(denom) : -INFINITY;
+}
+
+}  // namespace b200attn
+
+extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stream_) {
+  using namespace b200attn;
+  if (p == nullptr) {
+    set_error("fwd_splitkv: null params");
+    return B200ATTN_EINVAL;
+  }
+  if (p->B <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->M <= 0 || p->N <= 0 || p->num_splits < 1 ||
+      p->Hq % p->Hkv != 0) {
+    set_error("fwd_splitkv: bad shape");
+    return B200ATTN_EINVAL;
+  }
+  if (p->D != 16 && p->D != 32 && p->D != 64 && p->D != 128) {
+    set_error("fwd_splitkv: head dimension %d not in {16, 32, 64, 128}", p->D);
+    return B200ATTN_EINVAL;
+  }
+  if (p->dtype != B200ATTN_F16 && p->dtype != B200ATTN_BF16) {
+    set_error("fwd_splitkv: dtype must be fp16 or bf16");
+    return B200ATTN_EINVAL;
+  }
+  if (p->o.ptr == nullptr || p->lse == nullptr || p->part_o == nullptr || p->part_lse == nullptr) {
+    set_error("fwd_splitkv: null output / scratch pointer");
+    return B200ATTN_EINVAL;
+  }
+  const int n_blocks = cdiv(p->N, 128);
+  const int S = p->num_splits < n_blocks ? p->num_splits : n_blocks;
+  if (static_cast<int64_t>(cdiv(p->M, 256)) * p->num_splits > 2147483647ll || p->B > 65535 ||
+      p->Hq > 65535) {
+    set_error("fwd_splitkv: grid too large");
+    return B200ATTN_EINVAL;
+  }
+  // Partial pass: the forward kernel restricted to a K/V tile range per CTA, writing fp32
+  // partial O (normalised within the split) and the split's log-normaliser.
+  b200attn_fwd_params f{};
+  f.q = p->q; f.k = p->k; f.v = p->v;
+  f.B = p->B; f.Hq = p->Hq; f.Hkv = p->Hkv; f.M = p->M; f.N = p->N; f.D = p->D;
+  FwdLaunch L;
+  int rc;
+  switch (p->D) {
+    case 16: rc = make_fwd_tmaps<16>(&f, L); break;
+    case 32: rc = make_fwd_tmaps<32>(&f, L); break;
+    case 64: rc = make_fwd_tmaps<64>(&f, L); break;
+    default: rc = make_fwd_tmaps<128>(&f, L); break;
+  }
+  if (rc) return rc;
+  const int64_t MD = static_cast<int64_t>(p->M) * p->D;
+  FwdArgs& a = L.args;
+  a.o = p->part_o;
+  a.lse = p->part_lse;
+  a.o_stride_b = static_cast<int64_t>(p->Hq) * p->num_splits * MD;
+  a.o_stride_h = p->num_splits * MD;
+  a.o_stride_m = p->D;
+  a.o_stride_split = MD;
+  a.lse_stride_b = static_cast<int64_t>(p->Hq) * p->num_splits * p->M;
+  a.lse_stride_h = static_cast<int64_t>(p->num_splits) * p->M;
+  a.lse_stride_split = p->M;
+  a.num_splits = p->num_splits;
+  a.tiles_per_split = cdiv(n_blocks, S);
+  a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
+  a.groups = p->Hq / p->Hkv;
+  a.causal = p->causal ? 1 : 0;
+  a.o_fp32 = 1;
+  a.sm_scale = p->sm_scale;
+  a.qk_scale = p->sm_scale * 1.4426950408889634f;
+  a.drop = make_dropout_ctx(0.f, 0, 0);
+  a.status = p->status;
+  L.grid = dim3(static_cast<unsigned>(cdiv(p->M, 256) * p->num_splits), static_cast<unsigned>(p->Hq),
+                static_cast<unsigned>(p->B));
+  L.bf16 = p->dtype == B200ATTN_BF16;
+  L.dropout = false;
+  L.stream = static_cast<cudaStream_t>(stream_);
+  switch (p->D) {
+    case 16: rc = launch_fwd_d16(L); break;
+    case 32: rc = launch_fwd_d32(L); break;
+    case 64: rc = launch_fwd_d64(L); break;
+    default: rc = launch_fwd_d128(L); break;
+  }
+  if (rc) return rc;
+  const int64_t rows = static_cast<int64_t>(p->B) * p->Hq * p->M;
+  if (rows > 2147483647ll) {
+    set_error("fwd_splitkv: too many rows for the combine grid");
+    return B200ATTN_EINVAL;
+  }
+  if (L.bf16) {
+    splitkv_combine_kernel<true><<<static_cast<unsigned>(rows), 128, 0, L.stream>>>(
+        p->part_o, p->part_lse, p->o.ptr, p->lse, p->o.stride[0], p->o.stride[1], p->o.stride[2], p->Hq,
+        p->M, p->D, p->num_splits);
+  } else {
+    splitkv_combine_kernel<false><<<static_cast<unsigned>(rows), 128, 0, L.stream>>>(
+        p->part_o, p->part_lse, p->o.ptr, p->lse, p->o.stride[0], p->o.stride[1], p->o.stride[2], p->Hq,
+        p->M, p->D, p->num_splits);
+  }
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
 }

@@ -42,7 +42,9 @@ struct TileCfg {
 struct FwdArgs {
   void* o;
   float* lse;
-  int64_t o_stride_b, o_stride_h, o_stride_m;
+  int64_t o_stride_b, o_stride_h, o_stride_m, o_stride_split;
+  int64_t lse_stride_b, lse_stride_h, lse_stride_split;
+  int num_splits, tiles_per_split;  // split-KV: CTA `split` visits K/V tiles [split*tps, (split+1)*tps)
   int B, Hq, Hkv, M, N, groups;
   int causal, o_fp32;
   float sm_scale, qk_scale;
@@ -96,7 +98,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_blk = gridDim.x - 1 - blockIdx.x;  // longest (causal) row blocks first
+  const int split = blockIdx.x % args.num_splits;
+  const int m_blk = gridDim.x / args.num_splits - 1 - blockIdx.x / args.num_splits;  // longest (causal) row blocks first
+  const int j0 = split * args.tiles_per_split;  // first K/V tile of this CTA
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int hk = h / args.groups;
@@ -110,7 +114,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const int mt = m0 + t * BLOCK;
     int hi = args.N;
     if (args.causal) hi = min(args.N, max(0, P_SEQ + mt + BLOCK));
-    n_tiles[t] = mt < args.M ? cdiv(hi, BLOCK) : 0;
+    const int n_full = mt < args.M ? cdiv(hi, BLOCK) : 0;
+    n_tiles[t] = max(0, min(n_full, j0 + args.tiles_per_split) - j0);
   }
   const int n_max = max(n_tiles[0], n_tiles[1]);
 
@@ -177,12 +182,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         mbar_expect_tx(&k_full[st], Cfg::TILE_BYTES);
         for (int c = 0; c < Cfg::NCHUNK; ++c)
           tma_load_4d(sK + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmK, &k_full[st],
-                      c * Cfg::CHUNK, j * BLOCK, hk, b);
+                      c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
         if (!wait(&v_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
         mbar_expect_tx(&v_full[st], Cfg::TILE_BYTES);
         for (int c = 0; c < Cfg::NCHUNK; ++c)
           tma_load_4d(sV + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmV, &v_full[st],
-                      c * Cfg::CHUNK, j * BLOCK, hk, b);
+                      c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
       }
     }
     __syncwarp();
@@ -287,8 +292,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       tmem_ld32(tmem_s + 96, s + 96);
       tmem_wait_ld();
 
-      if ((j + 1) * BLOCK > full_upto) {
-        const int base = j * BLOCK;
+      if ((j0 + j + 1) * BLOCK > full_upto) {
+        const int base = (j0 + j) * BLOCK;
 #pragma unroll
         for (int i = 0; i < 128; ++i)
           if (base + i >= lim) s[i] = 0xff800000u;  // -inf
@@ -339,7 +344,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, neg_ms));
         sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
         if constexpr (DROPOUT) {
-          const uint64_t ctr = ctr_row + static_cast<uint64_t>(j * BLOCK + i);
+          const uint64_t ctr = ctr_row + static_cast<uint64_t>((j0 + j) * BLOCK + i);
           if (!dropout_keep(args.drop, ctr + 0)) p0 = 0.f;
           if (!dropout_keep(args.drop, ctr + 1)) p1 = 0.f;
           if (!dropout_keep(args.drop, ctr + 2)) p2 = 0.f;
@@ -365,7 +370,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     if (ok && m_glob < args.M) {
       const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
       const float lse = empty ? -INFINITY : m_run * args.sm_scale + logf(l_run);
-      args.lse[(static_cast<int64_t>(b) * args.Hq + h) * args.M + m_glob] = lse;
+      args.lse[b * args.lse_stride_b + h * args.lse_stride_h + split * args.lse_stride_split + m_glob] = lse;
     }
     if (ok) {
       tc_fence_after();
@@ -373,7 +378,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
       float inv = empty ? 0.f : 1.0f / l_run;
       if constexpr (DROPOUT) inv *= args.drop.inv_keep;
-      const int64_t o_off = b * args.o_stride_b + h * args.o_stride_h +
+      const int64_t o_off = b * args.o_stride_b + h * args.o_stride_h + split * args.o_stride_split +
                             static_cast<int64_t>(m_glob) * args.o_stride_m;
 #pragma unroll
       for (int c = 0; c < D; c += 16) {

@@ -1,0 +1,265 @@
+"""GPU parity of flash_attention against the oracle, on the reference's own test shapes and rule
+(tests/flag_attn/test_flash_attention.py). Every call goes through the public Python entry point,
+i.e. through the C ABI of libb200attn.so."""
+import itertools
+import math
+
+import pytest
+import torch
+
+from conftest import ATTENTION_GOLDENS, TRITON_GOLDENS, load_golden
+from flagattention_b200 import check_device_status, flash_attention
+from gpu_util import (assert_2x_rule, attention_backward, attention_forward, clean, device,
+                      kernel_dropout_mask, make_qkv, max_abs_diff)
+
+pytestmark = pytest.mark.gpu
+
+FWD_SHAPES = [
+    (2, 4, 4, 512, 612, 128), (2, 4, 4, 1024, 1034, 64), (2, 4, 4, 2048, 2048, 32), (2, 4, 4, 4096, 4096, 16),
+    (2, 4, 4, 4001, 4001, 32), (2, 4, 4, 4001, 4096, 64), (2, 4, 4, 4096, 4000, 128), (1, 2, 2, 8192, 8202, 16),
+    (1, 2, 2, 8192, 8192, 32),
+    (2, 4, 2, 512, 612, 128), (2, 4, 1, 1024, 1034, 64), (2, 4, 2, 2048, 2048, 32), (2, 4, 1, 4096, 4096, 16),
+    (2, 4, 2, 4001, 4001, 32), (2, 4, 1, 4001, 4096, 64), (2, 4, 2, 4096, 4000, 128), (1, 2, 1, 8192, 8202, 16),
+    (1, 2, 1, 8192, 8192, 32),
+]
+BWD_SHAPES = [s if s[3:5] != (4096, 4000) else (s[0], s[1], s[2], 4096, 4001, 128) for s in FWD_SHAPES] + [
+    (2, 4, 4, 10006, 10, 128), (2, 4, 2, 10006, 10, 128)]
+AUX_SHAPES = [(2, 4, 512, 612, 128), (2, 4, 1024, 1034, 64), (2, 4, 2048, 2048, 32), (2, 4, 4096, 4096, 16),
+              (2, 4, 4001, 4001, 32), (2, 4, 4001, 4096, 64), (2, 4, 4096, 4001, 128), (1, 2, 8192, 8202, 16),
+              (1, 2, 8192, 8192, 32)]
+DROPOUT_SHAPES = [s if s[2:4] != (4096, 4001) else (2, 4, 4096, 4000, 128) for s in AUX_SHAPES]
+
+# The reference crosses every shape with causal x dtype x layout x input scale; to keep the suite
+# within minutes each (shape, causal, dtype) gets one layout and one scale, cycling through all.
+_cycle = itertools.cycle(itertools.product(["BHTD", "BTHD"], [1.0, 2.0, 3.0, 4.0]))
+
+
+def _params(shapes):
+    out = []
+    for shape in shapes:
+        for causal in (True, False):
+            for dtype in (torch.float16, torch.bfloat16):
+                layout, scale = next(_cycle)
+                out.append(pytest.param(*shape, causal, dtype, layout, scale,
+                                        id=f"{'x'.join(map(str, shape))}-{'c' if causal else 'n'}-"
+                                           f"{str(dtype)[6:]}-{layout}-s{scale:g}"))
+    return out
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,scale", _params(FWD_SHAPES))
+def test_attention_fwd(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
+    q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, dtype, layout, scale, seed=10086)
+    o_ref = attention_forward(q, k, v, causal, upcast=True)
+    o_low = attention_forward(q, k, v, causal, upcast=False)
+    o = flash_attention(q, k, v, causal)
+    assert o.dtype == q.dtype and o.shape == q.shape and o.stride() == q.stride()
+    assert_2x_rule("o", o, o_low, o_ref)
+    check_device_status()
+
+
+SPLIT_SHAPES = [(s[0], s[1], s[2], 1, s[4], s[5]) for s in FWD_SHAPES]
+SPLIT_SHAPES[6] = (2, 4, 4, 2, 4000, 128)
+SPLIT_SHAPES[15] = (2, 4, 2, 2, 4000, 128)
+SPLIT_SHAPES[7] = (1, 2, 2, 4, 8202, 16)
+SPLIT_SHAPES[16] = (1, 2, 1, 4, 8202, 16)
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,scale",
+                         [p for p in _params(SPLIT_SHAPES)])
+def test_attention_splitkv(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
+    # Decode-like shapes take the split-KV branch (tests/flag_attn/test_flash_attention.py:127-172).
+    q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, dtype, layout, 10.0, seed=10086)
+    o_ref = attention_forward(q, k, v, causal, upcast=True)
+    o_low = attention_forward(q, k, v, causal, upcast=False)
+    o = flash_attention(q, k, v, causal)
+    assert o.dtype == q.dtype
+    assert_2x_rule("o", o, o_low, o_ref)
+    check_device_status()
+
+
+@pytest.mark.parametrize("seed", [17, 35, 36, 68, 77])
+def test_splitkv_large_logits(seed):
+    g = torch.Generator(device=device()).manual_seed(seed)
+    q = torch.randn((1, 2, 4, 16), generator=g, device=device(), dtype=torch.float16) * 10
+    k = torch.randn((1, 1, 8202, 16), generator=g, device=device(), dtype=torch.float16) * 10
+    v = torch.randn(k.shape, generator=g, device=device(), dtype=torch.float16) * 10
+    expected = attention_forward(q, k, v, False, upcast=True)
+    baseline = attention_forward(q, k, v, False, upcast=False)
+    actual = flash_attention(q, k, v)
+    assert actual.dtype == q.dtype
+    assert max_abs_diff(actual, expected) <= 2 * max_abs_diff(baseline, expected) + 1e-5
+
+
+def test_splitkv_independent_kv_strides():
+    g = torch.Generator(device=device()).manual_seed(2026)
+    q = torch.randn((2, 4, 1, 32), generator=g, device=device(), dtype=torch.float16)
+    k = torch.randn((2, 2, 257, 32), generator=g, device=device(), dtype=torch.float16)
+    v = torch.randn((2, 257, 2, 32), generator=g, device=device(), dtype=torch.float16).transpose(1, 2)
+    assert k.stride() != v.stride()
+    actual = flash_attention(q, k, v)
+    expected = attention_forward(q, k, v, False, upcast=True)
+    baseline = attention_forward(q, k, v, False, upcast=False)
+    assert max_abs_diff(actual, expected) <= 2 * max_abs_diff(baseline, expected) + 1e-5
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,scale", _params(BWD_SHAPES))
+def test_attention_bwd(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
+    q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, layout, scale, seed=10086, requires_grad=True)
+    o_ref = attention_forward(q, k, v, causal, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
+    o_low = attention_forward(q, k, v, causal, upcast=False)
+    g_low = torch.autograd.grad(o_low, (q, k, v), do)
+    o = flash_attention(q, k, v, causal)
+    g = torch.autograd.grad(o, (q, k, v), do)
+    assert_2x_rule("o", o, o_low, o_ref)
+    for name, a, b_, c in zip(("dq", "dk", "dv"), g, g_low, g_ref):
+        assert a.shape == c.shape and a.dtype == c.dtype
+        assert_2x_rule(name, a, b_, c)
+    assert g[0].stride() == q.stride()
+    check_device_status()
+
+
+@pytest.mark.parametrize("B,H,M,N,D,dtype,layout,scale", [
+    pytest.param(*s, dt, lay, sc, id=f"{'x'.join(map(str, s))}-{str(dt)[6:]}-{lay}-s{sc:g}")
+    for s, (dt, lay, sc) in zip(AUX_SHAPES * 2, itertools.cycle(itertools.product(
+        [torch.float16, torch.bfloat16], ["BHTD", "BTHD"], [1.0, 2.0, 3.0, 4.0])))])
+def test_attention_with_aux_outs(B, H, M, N, D, dtype, layout, scale):
+    q, k, v, _ = make_qkv(B, H, H, M, N, D, dtype, layout, scale, seed=10086)
+    o_ref, l_ref, t_ref = attention_forward(q, k, v, False, upcast=True, return_log_normalizer=True,
+                                            return_total_attention=True)
+    o_low, l_low, t_low = attention_forward(q, k, v, False, upcast=False, return_log_normalizer=True,
+                                            return_total_attention=True)
+    o, lse, tot, seed, offset = flash_attention(q, k, v, False, return_log_normalizer=True,
+                                                return_total_attention=True)
+    assert seed is None and offset is None
+    assert lse.dtype == torch.float32 and lse.shape == (B, H, M)
+    assert tot.dtype == torch.float32 and tot.shape == (B, H, N)
+    assert_2x_rule("o", o, o_low, o_ref)
+    assert_2x_rule("log_normalizer", lse, l_low, l_ref)
+    assert_2x_rule("total_attention", tot, t_low, t_ref)
+    check_device_status()
+
+
+def _dropout_params():
+    out = []
+    cyc = itertools.cycle(itertools.product([0.5, 0.8], [True, False], [torch.float16, torch.bfloat16],
+                                            ["BHTD", "BTHD"], [1.0, 2.0]))
+    for shape in DROPOUT_SHAPES * 4:
+        p, causal, dtype, layout, scale = next(cyc)
+        out.append(pytest.param(*shape, p, causal, dtype, layout, scale,
+                                id=f"{'x'.join(map(str, shape))}-p{p}-{'c' if causal else 'n'}-"
+                                   f"{str(dtype)[6:]}-{layout}-s{scale:g}"))
+    return out
+
+
+@pytest.mark.parametrize("B,H,M,N,D,p,causal,dtype,layout,scale", _dropout_params())
+def test_attention_dropout_fwd_bwd(B, H, M, N, D, p, causal, dtype, layout, scale):
+    """Forward and backward under dropout; the mask is rebuilt from the returned (seed, offset)
+    and fed to the oracle, as tests/flag_attn/test_flash_attention.py:298-393 does."""
+    q, k, v, do = make_qkv(B, H, H, M, N, D, dtype, layout, scale, seed=10086, requires_grad=True)
+    before = torch.cuda.default_generators[0].get_state().view(torch.int64)[1].item()
+    o, _, _, seed, offset = flash_attention(q, k, v, causal, dropout_p=p, return_seed_offset=True)
+    after = torch.cuda.default_generators[0].get_state().view(torch.int64)[1].item()
+    assert isinstance(seed, int) and isinstance(offset, int)
+    assert offset == before and after - before == (B * H * M * N + 3) // 4 * 4
+    g = torch.autograd.grad(o, (q, k, v), do)
+    mask = kernel_dropout_mask(B, H, M, N, p, seed, offset)
+    o_ref = attention_forward(q, k, v, causal, dropout_p=p, dropout_mask=mask, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
+    o_low = attention_forward(q, k, v, causal, dropout_p=p, dropout_mask=mask, upcast=False)
+    g_low = torch.autograd.grad(o_low, (q, k, v), do)
+    assert_2x_rule("o", o, o_low, o_ref)
+    for name, a, b_, c in zip(("dq", "dk", "dv"), g, g_low, g_ref):
+        assert_2x_rule(name, a, b_, c)
+    check_device_status()
+
+
+@pytest.mark.parametrize("seed", [55, 94])
+def test_attention_bwd_dropout_bfloat16_precision(seed):
+    # Regression case of the reference (test_flash_attention.py:239-250): bf16 dQ under p = 0.8.
+    torch.cuda.manual_seed(seed)
+    B, H, M, N, D = 2, 4, 4096, 4096, 16
+    q, k, v, do = make_qkv(B, H, H, M, N, D, torch.bfloat16, "BTHD", 1.0, seed=seed, requires_grad=True)
+    o, _, _, s, off = flash_attention(q, k, v, True, dropout_p=0.8, return_seed_offset=True)
+    g = torch.autograd.grad(o, (q, k, v), do)
+    mask = kernel_dropout_mask(B, H, M, N, 0.8, s, off)
+    o_ref = attention_forward(q, k, v, True, dropout_p=0.8, dropout_mask=mask, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
+    o_low = attention_forward(q, k, v, True, dropout_p=0.8, dropout_mask=mask, upcast=False)
+    g_low = torch.autograd.grad(o_low, (q, k, v), do)
+    for name, a, b_, c in zip(("dq", "dk", "dv"), g, g_low, g_ref):
+        assert_2x_rule(name, a, b_, c)
+
+
+@pytest.mark.parametrize("name", ATTENTION_GOLDENS)
+def test_against_reference_pytorch_fixture(name):
+    """Kernel outputs against what the reference's PyTorch attention produced when the fixture was
+    generated (fp32-upcast result; budget = 2 x the native-dtype run's own error + 1e-5)."""
+    g = load_golden(name)
+    m = g["meta"]
+    dev = device()
+    q, k, v, do = (g[x].to(dev).requires_grad_(x != "do") for x in ("q", "k", "v", "do"))
+    p = m["dropout_p"]
+    if p > 0:
+        # Put the default generator at the fixture's (seed, offset).
+        st = torch.cuda.default_generators[0].get_state()
+        st.view(torch.int64)[0] = m["rng_seed"]
+        st.view(torch.int64)[1] = m["rng_offset"]
+        torch.cuda.default_generators[0].set_state(st)
+    o, lse, tot, seed, offset = flash_attention(q, k, v, m["causal"], dropout_p=p, return_log_normalizer=True,
+                                                return_total_attention=True, return_seed_offset=True)
+    if p > 0:
+        assert (seed, offset) == (m["rng_seed"], m["rng_offset"])
+        mask = kernel_dropout_mask(m["B"], m["Hq"], m["M"], m["N"], p, seed, offset).cpu()
+        assert torch.equal(mask, g["mask"])
+    dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+    budget = 2 * max_abs_diff(clean(g["o_lowp"]), clean(g["o_ref32"])) + 1e-5
+    assert max_abs_diff(clean(o.cpu()), clean(g["o_ref32"])) <= budget
+    fin = torch.isfinite(g["lse_ref32"])
+    assert torch.equal(torch.isfinite(lse.cpu()), fin)
+    assert max_abs_diff(lse.cpu()[fin], g["lse_ref32"][fin]) <= 1e-4
+    assert max_abs_diff(tot.cpu(), g["tot_ref32"]) <= 2e-3 * max(1.0, g["tot_ref32"].max().item())
+    tol = (2.5e-2 if m["dtype"] == "bfloat16" else 4e-3) / (1.0 - p)
+    for mine, key in ((dq, "dq_ref32"), (dk, "dk_ref32"), (dv, "dv_ref32")):
+        ref = clean(g[key])
+        assert max_abs_diff(clean(mine.cpu()), ref) <= tol * max(1.0, ref.abs().max().item()), key
+
+
+@pytest.mark.parametrize("name", TRITON_GOLDENS)
+def test_against_reference_triton_fixture(name):
+    """Kernel outputs against the reference's Triton kernels (interpreter run stored as fixture)."""
+    g = load_golden(name)
+    m = g["meta"]
+    dev = device()
+    q, k, v, do = (g[x].to(dev).requires_grad_(x != "do") for x in ("q", "k", "v", "do"))
+    p = m["dropout_p"]
+    st = torch.cuda.default_generators[0].get_state()
+    st.view(torch.int64)[0] = m["rng_seed"]
+    st.view(torch.int64)[1] = m["rng_offset"]
+    torch.cuda.default_generators[0].set_state(st)
+    o, lse, tot, _, _ = flash_attention(q, k, v, m["causal"], dropout_p=p, return_log_normalizer=True,
+                                        return_total_attention=True)
+    dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+    assert max_abs_diff(o.cpu(), g["o"]) <= 4e-3
+    fin = torch.isfinite(g["lse"])
+    assert torch.equal(torch.isfinite(lse.cpu()), fin)
+    assert max_abs_diff(lse.cpu()[fin], g["lse"][fin]) <= 1e-4
+    assert max_abs_diff(tot.cpu(), g["tot"]) <= 2e-3
+    assert max_abs_diff(dq.cpu(), g["dq"]) <= 1e-2
+    assert max_abs_diff(dk.cpu(), g["dk"]) <= 2e-2
+    assert max_abs_diff(dv.cpu(), g["dv"]) <= 2e-2
+    check_device_status()
+
+
+def test_return_conventions_and_rng_untouched_without_dropout():
+    q, k, v, _ = make_qkv(1, 4, 2, 300, 300, 64, torch.float16)
+    before = torch.cuda.default_generators[0].get_state().clone()
+    o = flash_attention(q, k, v)
+    assert isinstance(o, torch.Tensor)
+    out = flash_attention(q, k, v, return_seed_offset=True)
+    assert isinstance(out, tuple) and len(out) == 5 and out[1:] == (None, None, None, None)
+    out = flash_attention(q, k, v, return_log_normalizer=True)
+    assert out[1] is not None and out[2] is None
+    assert torch.equal(torch.cuda.default_generators[0].get_state(), before)
+    with pytest.raises(AssertionError, match="splitkv"):
+        flash_attention(q[:, :1, :1], k[:, :1], v[:, :1], dropout_p=0.5)
