@@ -1,0 +1,439 @@
+"""Benchmark of the flash_attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config NAME]
+
+One "step" is one forward + backward of the workload over a batch of synthetic, seeded inputs.
+The default workload is the Llama-style GQA prefill training step the headline metric is quoted on:
+B=4, Hq=32, Hkv=8, M=N=4096, D=128, bf16, causal, log-normaliser returned.
+
+* ``value`` is aggregate algorithmic TFLOPS (reference convention: forward 4*B*Hq*M*N*D, backward
+  2.5x that, causal x0.5) over all ranks with inputs resident in HBM; timing is CUDA events around
+  exactly K steps, barrier + synchronize on both sides, max over ranks.
+* ``e2e`` is the same metric with HOST (pinned) inputs and outputs: every step copies q, k, v, dO to
+  the device and o, lse, dq, dk, dv back inside the timed region.
+* ``roofline`` describes the dominant kernel of the step, timed by itself through the C ABI.
+* ``cpu_baseline`` times the CPU oracle (the reference's PyTorch attention restated) on a bounded
+  sample of the same workload on this host's cores.
+* ``--impl reference`` runs only that CPU path (all host threads) and prints its own line.
+
+N > 1: launched under torchrun, one rank per GPU; every rank runs the full per-GPU workload
+(independent (batch x KV-head-group) units, no collective on the data path), so scaling is weak.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CONFIGS = {
+    # name: B, Hq, Hkv, M, N, D, dtype, causal, dropout_p, mode
+    "c2_gqa_prefill_train": dict(B=4, Hq=32, Hkv=8, M=4096, N=4096, D=128, dtype="bfloat16", causal=True,
+                                 dropout_p=0.0, mode="fwd+bwd"),
+    "c3_d64_dropout_aux": dict(B=16, Hq=16, Hkv=16, M=2048, N=2048, D=64, dtype="float16", causal=False,
+                               dropout_p=0.1, mode="fwd+bwd"),
+    "c4_mqa_cross_fwd": dict(B=8, Hq=16, Hkv=1, M=512, N=8192, D=128, dtype="bfloat16", causal=False,
+                             dropout_p=0.0, mode="fwd"),
+    "c5_long_context_fwd": dict(B=1, Hq=64, Hkv=8, M=32768, N=32768, D=128, dtype="bfloat16", causal=True,
+                                dropout_p=0.0, mode="fwd"),
+}
+DEFAULT_CONFIG = "c2_gqa_prefill_train"
+
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel on the default
+# workload, from the ncu capture summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES = {"c2_gqa_prefill_train": None}
+
+
+def fwd_flops(cfg) -> float:
+    f = 4.0 * cfg["B"] * cfg["Hq"] * cfg["M"] * cfg["N"] * cfg["D"]
+    return f * 0.5 if cfg["causal"] else f
+
+
+def step_flops(cfg) -> float:
+    return fwd_flops(cfg) * (3.5 if cfg["mode"] == "fwd+bwd" else 1.0)
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------ clocks sampling
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.tmp = None
+
+    def start(self):
+        exe = shutil.which("nvidia-smi")
+        if exe is None:
+            return
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = subprocess.Popen(
+            [exe, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i",
+             str(self.gpu_index)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = []
+        for line in Path(self.tmp.name).read_text().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 7:
+                rows.append(parts)
+        os.unlink(self.tmp.name)
+        if not rows:
+            return None
+        sm = []
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+            except ValueError:
+                pass
+        reasons = []
+        for idx, name in ((3, "hw_slowdown"), (4, "hw_thermal_slowdown"), (5, "sw_thermal_slowdown"),
+                          (6, "sw_power_cap")):
+            if any(r[idx].lower().startswith("active") for r in rows):
+                reasons.append(name)
+        try:
+            sm_max = float(rows[0][1])
+        except ValueError:
+            sm_max = None
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": sm_max,
+                "reasons": reasons, "samples": len(rows)}
+
+
+# ------------------------------------------------------------------ workload
+def make_inputs(cfg, device, seed):
+    dtype = getattr(torch, cfg["dtype"])
+    g = torch.Generator(device=device).manual_seed(seed)
+    B, Hq, Hkv, M, N, D = (cfg[k] for k in ("B", "Hq", "Hkv", "M", "N", "D"))
+    q = torch.randn(B, Hq, M, D, device=device, dtype=dtype, generator=g)
+    k = torch.randn(B, Hkv, N, D, device=device, dtype=dtype, generator=g)
+    v = torch.randn(B, Hkv, N, D, device=device, dtype=dtype, generator=g)
+    do = torch.randn(B, Hq, M, D, device=device, dtype=dtype, generator=g)
+    return q, k, v, do
+
+
+def run_step(cfg, q, k, v, do):
+    """One pass of the hot path through the public API; returns every tensor the step produces."""
+    from flagattention_b200 import flash_attention
+    if cfg["mode"] == "fwd":
+        o = flash_attention(q, k, v, causal=cfg["causal"], dropout_p=cfg["dropout_p"])
+        return (o,)
+    q = q.detach().requires_grad_(True)
+    k = k.detach().requires_grad_(True)
+    v = v.detach().requires_grad_(True)
+    o, lse, _, _, _ = flash_attention(q, k, v, causal=cfg["causal"], dropout_p=cfg["dropout_p"],
+                                      return_log_normalizer=True)
+    dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+    return o, lse, dq, dk, dv
+
+
+def kernels_per_step(cfg) -> int:
+    # forward: 1 kernel; backward: delta, statistics, dK/dV kernel, dQ kernel.
+    return 1 + (4 if cfg["mode"] == "fwd+bwd" else 0)
+
+
+def time_kernels(cfg, q, k, v, do, iters=5):
+    """Times the library's kernels one by one through the C ABI (CUDA events on the launching
+    stream) and returns {name: ms}."""
+    from flagattention_b200 import _lib
+    lib = _lib.load()
+    dev = q.device
+    B, Hq, Hkv, M, N, D = (cfg[x] for x in ("B", "Hq", "Hkv", "M", "N", "D"))
+    dt = _lib.dtype_code(q.dtype)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    o = torch.empty_like(q)
+    lse = torch.empty(B, Hq, M, dtype=torch.float32, device=dev)
+    sm_scale = 1.0 / math.sqrt(D)
+    fp = _lib.FwdParams(_lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), lse.data_ptr(),
+                        B, Hq, Hkv, M, N, D, dt, dt, int(cfg["causal"]), sm_scale, float(cfg["dropout_p"]),
+                        12345, 0, status.data_ptr())
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / iters
+
+    out = {"fwd_kernel": timed(lambda: _lib.check(lib.b200attn_fwd(fp, stream), "fwd"))}
+    if cfg["mode"] == "fwd+bwd":
+        dq = torch.empty_like(q)
+        dk = torch.empty_like(k)
+        dv = torch.empty_like(v)
+        delta = torch.empty_like(lse)
+        ws = torch.empty(lib.b200attn_bwd_workspace_bytes(B, Hq, Hkv, M, N, D) // 4, dtype=torch.float32,
+                         device=dev)
+        bp = _lib.BwdParams(_lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o),
+                            _lib.tensor4(do), _lib.tensor4(dq), _lib.tensor4(dk), _lib.tensor4(dv),
+                            lse.data_ptr(), delta.data_ptr(), ws.data_ptr(), B, Hq, Hkv, M, N, D, dt, dt,
+                            int(cfg["causal"]), sm_scale, float(cfg["dropout_p"]), 12345, 0,
+                            status.data_ptr())
+        for name, mask in (("bwd_prep_kernels", 1), ("bwd_kernel<kv>", 2), ("bwd_kernel<q>", 4)):
+            out[name] = timed(lambda m=mask: _lib.check(lib.b200attn_bwd_stages(bp, stream, m), name))
+    assert status.item() == 0, "a kernel reported a device-side wait timeout"
+    return out
+
+
+# ------------------------------------------------------------------ CPU baseline (oracle)
+def cpu_slice_inputs(cfg, seed=0):
+    """One (batch, KV-head-group) unit of the workload as CPU tensors."""
+    dtype = getattr(torch, cfg["dtype"])
+    g = torch.Generator().manual_seed(seed)
+    G = cfg["Hq"] // cfg["Hkv"]
+    q = torch.randn(1, G, cfg["M"], cfg["D"], generator=g).to(dtype)
+    k = torch.randn(1, 1, cfg["N"], cfg["D"], generator=g).to(dtype)
+    v = torch.randn(1, 1, cfg["N"], cfg["D"], generator=g).to(dtype)
+    do = torch.randn(1, G, cfg["M"], cfg["D"], generator=g).to(dtype)
+    return q, k, v, do
+
+
+def cpu_slice_step(cfg, q, k, v, do):
+    from oracle.attention import attention_forward
+    if cfg["mode"] == "fwd":
+        attention_forward(q, k, v, cfg["causal"], upcast=False)
+        return
+    q, k, v = (t.detach().requires_grad_(True) for t in (q, k, v))
+    o = attention_forward(q, k, v, cfg["causal"], upcast=False)
+    torch.autograd.grad(o, (q, k, v), do)
+
+
+def slice_flops(cfg) -> float:
+    return step_flops(cfg) / (cfg["B"] * cfg["Hkv"])
+
+
+def cpu_baseline(cfg, budget_s=12.0, max_slices=64):
+    """Times the oracle (native-dtype path, i.e. the reference's PyTorch CPU attention) on whole
+    (batch, KV-group) units until `budget_s` seconds or `max_slices` units have run."""
+    threads = torch.get_num_threads()
+    q, k, v, do = cpu_slice_inputs(cfg)
+    # long-context slices do not fit the budget: shrink the query rows of the sample and say so
+    rows = cfg["M"]
+    note = ""
+    if cfg["M"] * cfg["N"] > 4096 * 4096 * 4:
+        rows = max(128, (4096 * 4096 * 4) // cfg["N"])
+        q, do = q[:, :, -rows:], do[:, :, -rows:]
+        note = f", last {rows} query rows only (work scaled by rows)"
+    frac = rows / cfg["M"]
+    n = 0
+    t0 = time.perf_counter()
+    while n < max_slices and (n == 0 or time.perf_counter() - t0 < budget_s):
+        cpu_slice_step(cfg, q, k, v, do)
+        n += 1
+    dt = time.perf_counter() - t0
+    flops = slice_flops(cfg) * frac * n
+    if cfg["causal"] and frac < 1.0:
+        # the last rows of a causal problem see (almost) every key: x2 relative to the average row
+        flops = 4.0 * (cfg["Hq"] // cfg["Hkv"]) * rows * cfg["N"] * cfg["D"] * n * \
+            (3.5 if cfg["mode"] == "fwd+bwd" else 1.0)
+    return {"value": flops / dt * 1e-12, "unit": "TFLOPS", "cores": threads, "kind": "port",
+            "sample": f"{n} of {cfg['B'] * cfg['Hkv']} (batch, KV-group) units of the workload{note}, "
+                      f"{dt:.1f} s, native {cfg['dtype']} math, {os.cpu_count()} logical CPUs"}
+
+
+# ------------------------------------------------------------------ main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default=DEFAULT_CONFIG, choices=sorted(CONFIGS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config_desc = {"workload": args.config, **{k: cfg[k] for k in ("B", "Hq", "Hkv", "M", "N", "D", "dtype",
+                                                                  "causal", "dropout_p", "mode")},
+                   "sharding": "independent (batch x KV-head-group) units per rank, no collective",
+                   "l2_policy": "inputs+outputs per step exceed the 126 MB L2 (no flush needed)"}
+    metric = "flash_attention fwd+bwd TFLOPS (bf16 causal D=128)" if args.config == DEFAULT_CONFIG \
+        else f"flash_attention {cfg['mode']} TFLOPS ({args.config})"
+
+    if args.impl == "reference":
+        # The reference's own CPU implementation of the path (its PyTorch attention, restated in
+        # oracle/), all host threads, one (batch, KV-group) unit of the workload per step.
+        if rank != 0:
+            return
+        q, k, v, do = cpu_slice_inputs(cfg)
+        rows = cfg["M"]
+        if cfg["M"] * cfg["N"] > 4096 * 4096 * 4:
+            rows = max(128, (4096 * 4096 * 4) // cfg["N"])
+            q, do = q[:, :, -rows:], do[:, :, -rows:]
+        steps = max(1, min(args.steps, 6))
+        for _ in range(min(warmup, 1)):
+            cpu_slice_step(cfg, q, k, v, do)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            cpu_slice_step(cfg, q, k, v, do)
+        dt = time.perf_counter() - t0
+        per_step = slice_flops(cfg) * rows / cfg["M"]
+        if cfg["causal"] and rows < cfg["M"]:
+            per_step = 4.0 * (cfg["Hq"] // cfg["Hkv"]) * rows * cfg["N"] * cfg["D"] * \
+                (3.5 if cfg["mode"] == "fwd+bwd" else 1.0)
+        val = per_step * steps / dt * 1e-12
+        sample = (f"each step = 1 of {cfg['B'] * cfg['Hkv']} (batch, KV-group) units"
+                  + (f", last {rows} query rows" if rows < cfg["M"] else "") + f"; {steps} steps timed")
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": val, "unit": "TFLOPS", "n_gpus": args.gpus,
+            "steps": steps, "warmup": min(warmup, 1), "ms_per_step": dt / steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg["dtype"],
+            "data": "synthetic", "config": config_desc,
+            "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": torch.get_num_threads(),
+                             "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    q, k, v, do = make_inputs(cfg, device, seed=1000 + rank)
+    K = args.steps
+
+    # ---- device-resident timing --------------------------------------------------------------
+    for _ in range(warmup):
+        run_step(cfg, q, k, v, do)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        run_step(cfg, q, k, v, do)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+
+    # ---- end-to-end timing: host buffers, copies inside the timed region ----------------------
+    host_in = [t.cpu().pin_memory() for t in (q, k, v, do)]
+    outs = run_step(cfg, q, k, v, do)
+    host_out = [torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory() for t in outs]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+    dev_in = [torch.empty_like(t) for t in (q, k, v, do)]
+
+    def e2e_step():
+        for d, h in zip(dev_in, host_in):
+            d.copy_(h, non_blocking=True)
+        res = run_step(cfg, *dev_in)
+        for h, d in zip(host_out, res):
+            h.copy_(d, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(K):
+        e2e_step()
+    f1.record()
+    barrier()
+    ms_e2e_total = f0.elapsed_time(f1)
+
+    if dist is not None:
+        t = torch.tensor([ms_total, ms_e2e_total], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e_total = t.tolist()
+
+    # ---- per-kernel timing + roofline (rank 0) -------------------------------------------------
+    result = None
+    if rank == 0:
+        peaks, peak_src = load_peaks()
+        kern_ms = time_kernels(cfg, q, k, v, do)
+        f_fwd = fwd_flops(cfg)
+        # Algorithmic FLOPs per launch: forward 2 GEMMs; dK/dV kernel 4 of the backward's 5 GEMMs
+        # (S, dP, dV, dK); dQ kernel 1 (its S and dP are recomputation and not counted).
+        alg = {"fwd_kernel": f_fwd, "bwd_kernel<kv>": 2.0 * f_fwd, "bwd_kernel<q>": 0.5 * f_fwd}
+        dominant = max((n for n in kern_ms if n in alg), key=lambda n: kern_ms[n])
+        achieved = alg[dominant] / (kern_ms[dominant] * 1e-3) * 1e-12
+        peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+        value = step_flops(cfg) * K * world / (ms_total * 1e-3) * 1e-12
+        e2e_value = step_flops(cfg) * K * world / (ms_e2e_total * 1e-3) * 1e-12
+        result = {
+            "metric": metric, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": K,
+            "warmup": warmup, "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16" if cfg["dtype"] == "bfloat16" else "fp16",
+            "data": "synthetic", "config": config_desc,
+            "per_gpu_tflops": value / world, "tokens_per_s": cfg["B"] * cfg["M"] * K * world / (ms_total * 1e-3),
+            "frac_of_spec_peak_2250": value / world / 2250.0,
+            "frac_of_measured_burst_peak": value / world / float(peaks.get("bf16_tflops", 1590.0)),
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_total / K},
+            "gpu_launches": kernels_per_step(cfg) * K,
+            "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_src} sustained bf16",
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.config)},
+            "kernels_ms": kern_ms,
+            "kernels_alg_tflops": {n: alg[n] / (kern_ms[n] * 1e-3) * 1e-12 for n in alg if n in kern_ms},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            result["cpu_baseline"] = cpu_baseline(cfg)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if result is not None:
+        print(json.dumps(result))
+
+
+if __name__ == "__main__":
+    main()

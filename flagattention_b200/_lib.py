@@ -89,6 +89,7 @@ SYMBOLS = {
     "b200attn_total_attention": (c_int32, [POINTER(TotalParams), c_void_p]),
     "b200attn_bwd_workspace_bytes": (c_size_t, [c_int32] * 6),
     "b200attn_bwd": (c_int32, [POINTER(BwdParams), c_void_p]),
+    "b200attn_bwd_stages": (c_int32, [POINTER(BwdParams), c_void_p, c_int32]),
     "b200attn_bwd_delta": (c_int32, [POINTER(Tensor4), c_int32, POINTER(Tensor4), c_int32, c_void_p,
                                      c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200attn_dropout_mask": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_float, c_uint64,

@@ -64,7 +64,7 @@ static int dispatch(int D, const BwdLaunch& L) {
 }
 
 template <int D>
-static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t stream) {
+static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t stream, int stages) {
   BwdLaunch kv, qq;
   int rc;
   // MODE_KV: resident K, V (128-row boxes); streamed Q, dO (64-row boxes).
@@ -108,8 +108,9 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
   qq.mode = MODE_Q;
   qq.stream = stream;
 
-  if ((rc = dispatch(D, kv))) return rc;
-  return dispatch(D, qq);
+  if ((stages & B200ATTN_BWD_STAGE_KV) && (rc = dispatch(D, kv))) return rc;
+  if ((stages & B200ATTN_BWD_STAGE_Q) && (rc = dispatch(D, qq))) return rc;
+  return B200ATTN_OK;
 }
 
 template <int D>
@@ -156,6 +157,10 @@ extern "C" size_t b200attn_total_workspace_bytes(int32_t B, int32_t Hq, int32_t 
 }
 
 extern "C" int b200attn_bwd(const b200attn_bwd_params* p, void* stream_) {
+  return b200attn_bwd_stages(p, stream_, B200ATTN_BWD_STAGE_ALL);
+}
+
+extern "C" int b200attn_bwd_stages(const b200attn_bwd_params* p, void* stream_, int32_t stages) {
   using namespace b200attn;
   if (p == nullptr) {
     set_error("bwd: null params");
@@ -183,16 +188,18 @@ extern "C" int b200attn_bwd(const b200attn_bwd_params* p, void* stream_) {
     return B200ATTN_EINVAL;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  rc = b200attn_bwd_delta(&p->o, p->o_dtype, &p->d_o, p->dtype, p->delta, p->B, p->Hq, p->M, p->D, stream_);
-  if (rc) return rc;
   float2* stats = static_cast<float2*>(p->workspace);
-  rc = launch_stats(p->lse, p->delta, stats, p->B, p->Hq, p->M, pad128(p->M), stream);
-  if (rc) return rc;
+  if (stages & B200ATTN_BWD_STAGE_PREP) {
+    rc = b200attn_bwd_delta(&p->o, p->o_dtype, &p->d_o, p->dtype, p->delta, p->B, p->Hq, p->M, p->D, stream_);
+    if (rc) return rc;
+    rc = launch_stats(p->lse, p->delta, stats, p->B, p->Hq, p->M, pad128(p->M), stream);
+    if (rc) return rc;
+  }
   switch (p->D) {
-    case 16: return run_bwd<16>(p, stats, stream);
-    case 32: return run_bwd<32>(p, stats, stream);
-    case 64: return run_bwd<64>(p, stats, stream);
-    default: return run_bwd<128>(p, stats, stream);
+    case 16: return run_bwd<16>(p, stats, stream, stages);
+    case 32: return run_bwd<32>(p, stats, stream, stages);
+    case 64: return run_bwd<64>(p, stats, stream, stages);
+    default: return run_bwd<128>(p, stats, stream, stages);
   }
 }
 

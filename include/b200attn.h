@@ -106,6 +106,17 @@ size_t b200attn_bwd_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t 
                                     int32_t D);
 int b200attn_bwd(const b200attn_bwd_params* p, void* stream);
 
+/* The same backward restricted to some of its stages, so a profiler or benchmark can time the
+ * kernels one by one. PREP = delta + statistics preprocess, KV = the dK/dV kernel, Q = the dQ
+ * kernel; KV and Q need the scratch PREP wrote. No counterpart in the reference. */
+enum {
+  B200ATTN_BWD_STAGE_PREP = 1,
+  B200ATTN_BWD_STAGE_KV = 2,
+  B200ATTN_BWD_STAGE_Q = 4,
+  B200ATTN_BWD_STAGE_ALL = 7
+};
+int b200attn_bwd_stages(const b200attn_bwd_params* p, void* stream, int32_t stages);
+
 /* delta[b,h,m] = sum_d o*do in fp32: replaces `_bwd_preprocess` (flash.py:542-588). Also run
  * inside b200attn_bwd; exported for tests. */
 int b200attn_bwd_delta(const b200attn_tensor* o, int32_t o_dtype, const b200attn_tensor* d_o,
