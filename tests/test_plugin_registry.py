@@ -1,0 +1,67 @@
+"""install() against a stand-in that has the reference registry's shape (a package `flag_attn`
+with `runtime.backend.op_registry` and a vendor package), built in a temp dir so the test needs
+no reference checkout."""
+import importlib
+import sys
+import textwrap
+
+import pytest
+
+
+@pytest.fixture
+def fake_flag_attn(tmp_path, monkeypatch):
+    root = tmp_path / "flag_attn"
+    (root / "runtime" / "backend" / "_nvidia").mkdir(parents=True)
+    (root / "__init__.py").write_text(textwrap.dedent('''
+        import importlib
+        from . import runtime
+        _OPERATOR_EXPORTS = {"flash_attention": ("flag_attn.flash", "attention")}
+        def __getattr__(name):
+            module_name, attribute_name = _OPERATOR_EXPORTS[name]
+            value = runtime.backend.resolve_operator(name, module_name, attribute_name)
+            globals()[name] = value
+            return value
+    '''))
+    (root / "flash.py").write_text("def attention(*a, **k):\n    return 'generic'\n")
+    (root / "runtime" / "__init__.py").write_text(textwrap.dedent('''
+        from . import backend
+        class _Dev:
+            vendor_name = "nvidia"
+        device = _Dev()
+    '''))
+    (root / "runtime" / "backend" / "__init__.py").write_text("from .op_registry import resolve_operator\n")
+    (root / "runtime" / "backend" / "_nvidia" / "__init__.py").write_text("")
+    (root / "runtime" / "backend" / "op_registry.py").write_text(textwrap.dedent('''
+        from functools import lru_cache
+        from importlib import import_module
+        @lru_cache(maxsize=None)
+        def _backend_exports(vendor):
+            backend = import_module(f"flag_attn.runtime.backend._{vendor}")
+            exports = vars(backend).get("_OPERATOR_EXPORTS", {})
+            generic_only = vars(backend).get("_GENERIC_ONLY_OPS", ())
+            return {n: v for n, v in exports.items() if n not in generic_only}
+        @lru_cache(maxsize=None)
+        def _resolve_operator(name, generic_module, generic_name, vendor):
+            module_name, symbol = _backend_exports(vendor).get(name, (generic_module, generic_name))
+            return getattr(import_module(module_name), symbol)
+        def resolve_operator(name, generic_module, generic_name=None, *, vendor=None):
+            if vendor is None:
+                vendor = import_module("flag_attn.runtime").device.vendor_name
+            return _resolve_operator(name, generic_module, generic_name or name, vendor)
+    '''))
+    monkeypatch.syspath_prepend(str(tmp_path))
+    for mod in [m for m in sys.modules if m == "flag_attn" or m.startswith("flag_attn.")]:
+        monkeypatch.delitem(sys.modules, mod)
+    yield importlib.import_module("flag_attn")
+    for mod in [m for m in sys.modules if m == "flag_attn" or m.startswith("flag_attn.")]:
+        sys.modules.pop(mod, None)
+
+
+def test_install_and_uninstall(fake_flag_attn):
+    from flagattention_b200 import flash_attention, plugin
+    fa = fake_flag_attn
+    assert fa.flash_attention() == "generic"
+    plugin.install()
+    assert fa.flash_attention is flash_attention
+    plugin.uninstall()
+    assert fa.flash_attention() == "generic"
