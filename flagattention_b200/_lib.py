@@ -87,6 +87,7 @@ SYMBOLS = {
     "b200attn_fwd": (c_int32, [POINTER(FwdParams), c_void_p]),
     "b200attn_total_workspace_bytes": (c_size_t, [c_int32] * 3),
     "b200attn_total_attention": (c_int32, [POINTER(TotalParams), c_void_p]),
+    "b200attn_total_attention_static": (c_int32, [POINTER(TotalParams), c_void_p]),
     "b200attn_bwd_workspace_bytes": (c_size_t, [c_int32] * 6),
     "b200attn_bwd": (c_int32, [POINTER(BwdParams), c_void_p]),
     "b200attn_bwd_stages": (c_int32, [POINTER(BwdParams), c_void_p, c_int32]),

@@ -1,5 +1,7 @@
 // C entry points of the backward pass and of total attention: validation, TMA descriptors,
 // the preprocess launches and the dispatch on head dimension.
+#include <mutex>
+
 #include "bwd_launch.cuh"
 
 namespace b200attn {
@@ -231,3 +233,69 @@ extern "C" int b200attn_total_attention(const b200attn_total_params* p, void* st
   }
 }
 
+
+// ----------------------------------------------------- total attention without caller scratch
+namespace b200attn {
+
+// Per-query statistics scratch that lives inside the library image: B200ATTN_STATIC_STATS_MAX
+// (lse*log2e, delta) pairs = 4 MiB, resident on every GPU that loads the library until the
+// process exits. In host code this name only stands for the symbol; the device address is
+// looked up once per device with cudaGetSymbolAddress below.
+static __device__ __align__(256) float2 g_static_stats[B200ATTN_STATIC_STATS_MAX];
+
+static std::mutex g_static_stats_mutex;
+static float2* g_static_stats_ptr[64] = {};
+
+// Device address of g_static_stats on the current device (looked up on first use).
+static int static_stats_ptr(float2** out) {
+  int dev = 0;
+  B200ATTN_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_error("total_attention_static: device ordinal %d out of range", dev);
+    return B200ATTN_EUNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(g_static_stats_mutex);
+  if (g_static_stats_ptr[dev] == nullptr) {
+    float2* ptr = nullptr;
+    B200ATTN_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_stats));
+    g_static_stats_ptr[dev] = ptr;
+  }
+  *out = g_static_stats_ptr[dev];
+  return B200ATTN_OK;
+}
+
+}  // namespace b200attn
+
+extern "C" int b200attn_total_attention_static(const b200attn_total_params* p, void* stream_) {
+  using namespace b200attn;
+  if (p == nullptr) {
+    set_error("total_attention_static: null params");
+    return B200ATTN_EINVAL;
+  }
+  int rc = check_common("total_attention_static", p->B, p->Hq, p->Hkv, p->M, p->N, p->D, p->dtype);
+  if (rc) return rc;
+  if (p->lse == nullptr || p->tot == nullptr) {
+    set_error("total_attention_static: lse and tot must be non-null");
+    return B200ATTN_EINVAL;
+  }
+  const int64_t need = static_cast<int64_t>(p->B) * p->Hq * pad128(p->M);
+  if (need > B200ATTN_STATIC_STATS_MAX) {
+    set_error("total_attention_static: B*Hq*roundup(M,128) = %lld exceeds the built-in scratch of %d "
+              "entries; use b200attn_total_attention with caller scratch",
+              static_cast<long long>(need), B200ATTN_STATIC_STATS_MAX);
+    return B200ATTN_EUNSUPPORTED;
+  }
+  float2* stats = nullptr;
+  if ((rc = static_stats_ptr(&stats))) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  // Every entry the kernel reads ([0, need)) is rewritten here first, so whatever an earlier call
+  // left in the array never matters.
+  rc = launch_stats(p->lse, nullptr, stats, p->B, p->Hq, p->M, pad128(p->M), stream);
+  if (rc) return rc;
+  switch (p->D) {
+    case 16: return run_total<16>(p, stats, stream);
+    case 32: return run_total<32>(p, stats, stream);
+    case 64: return run_total<64>(p, stats, stream);
+    default: return run_total<128>(p, stats, stream);
+  }
+}

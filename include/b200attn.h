@@ -81,6 +81,22 @@ typedef struct {
 size_t b200attn_total_workspace_bytes(int32_t B, int32_t Hq, int32_t M);
 int b200attn_total_attention(const b200attn_total_params* p, void* stream);
 
+/* Total attention for callers that cannot hand the library any scratch memory, e.g. a serving
+ * process that gave its whole device-memory budget to its own pool at start-up, or a component
+ * that is only passed input and output buffers and has no allocator to ask. No counterpart in the
+ * reference. Same inputs, outputs and result as b200attn_total_attention; `workspace` is ignored.
+ * The per-query statistics go to an array built into the library (B200ATTN_STATIC_STATS_MAX
+ * entries, 4 MiB, held on every GPU that loads the library until the process exits), so the call
+ * makes no device allocation of any kind.
+ *  - Limit: B * Hq * roundup(M, 128) <= B200ATTN_STATIC_STATS_MAX, else B200ATTN_EUNSUPPORTED.
+ *  - The first call on each device looks up the array's device address; make that first call
+ *    outside any stream capture.
+ *  - All calls share the one array per GPU and the array keeps what the last call wrote. Each call
+ *    rewrites the part it reads before reading it, so nothing has to be cleared, but two calls
+ *    whose kernels may run at the same time on one GPU (different streams) race on it. */
+#define B200ATTN_STATIC_STATS_MAX 524288
+int b200attn_total_attention_static(const b200attn_total_params* p, void* stream);
+
 /* Backward: replaces `_bwd_preprocess`, `_bwd_kv_kernel`, `_bwd_q_kernel` and the GQA group
  * sum (flash.py:183-272, kernels flash.py:542-931).
  * `delta` [B,Hq,M] fp32 and `workspace` (b200attn_bwd_workspace_bytes() bytes, 16-byte aligned)
