@@ -56,7 +56,12 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel on the default
 # workload, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = {"c2_gqa_prefill_train": None}
+NCU_TRAFFIC_BYTES = {
+    # bwd_kernel<MODE_KV>: (170.5 + 22.9) MB measured at batch 2, scaled x2 to the batch-4 workload
+    # (traffic is proportional to batch); see profiles/fwd_kernel_bwd_kv_kernel_c2_batch2_full.md
+    "c2_gqa_prefill_train": {"bwd_kernel<kv>": 2 * (170.484224e6 + 22.904064e6),
+                             "fwd_kernel": 2 * (101.038336e6 + 32.596736e6)},
+}
 
 
 def fwd_flops(cfg) -> float:
@@ -279,8 +284,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default=DEFAULT_CONFIG, choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling runs)")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.batch > 0:
+        cfg["B"] = args.batch
     warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -364,6 +373,13 @@ def main():
     clocks = sampler.stop() if sampler else None
 
     # ---- end-to-end timing: host buffers, copies inside the timed region ----------------------
+    if args.no_e2e:
+        if rank == 0:
+            kern_ms = time_kernels(cfg, q, k, v, do, iters=1)
+            print(json.dumps({"profiling_run": True, "ms_per_step": ms_total / K, "kernels_ms": kern_ms}))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     host_in = [t.cpu().pin_memory() for t in (q, k, v, do)]
     outs = run_step(cfg, q, k, v, do)
     host_out = [torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory() for t in outs]
@@ -422,7 +438,8 @@ def main():
             "gpu_launches": kernels_per_step(cfg) * K,
             "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_src} sustained bf16",
-                         "traffic": NCU_TRAFFIC_BYTES.get(args.config)},
+                         "traffic": (NCU_TRAFFIC_BYTES.get(args.config) or {}).get(dominant)
+                         if args.batch == 0 else None},
             "kernels_ms": kern_ms,
             "kernels_alg_tflops": {n: alg[n] / (kern_ms[n] * 1e-3) * 1e-12 for n in alg if n in kern_ms},
         }
