@@ -25,8 +25,9 @@ static int check_common(const char* who, int B, int Hq, int Hkv, int M, int N, i
     set_error("%s: dtype must be fp16 or bf16", who);
     return B200ATTN_EINVAL;
   }
-  if (B > 65535 || Hq > 65535) {
-    set_error("%s: B and Hq are limited to 65535", who);
+  if (static_cast<int64_t>(B) * Hq * ((M + 127) / 128) > 2147483647ll ||
+      static_cast<int64_t>(B) * Hq * ((N + 127) / 128) > 2147483647ll) {
+    set_error("%s: problem exceeds the grid limit", who);
     return B200ATTN_EINVAL;
   }
   return B200ATTN_OK;
@@ -92,8 +93,9 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
   kv.args.out1_sb = p->dk.stride[0]; kv.args.out1_sh = p->dk.stride[1]; kv.args.out1_sr = p->dk.stride[2];
   kv.args.out2 = p->dv.ptr;
   kv.args.out2_sb = p->dv.stride[0]; kv.args.out2_sh = p->dv.stride[1]; kv.args.out2_sr = p->dv.stride[2];
-  kv.grid = dim3(static_cast<unsigned>(cdiv(p->N, 128)), static_cast<unsigned>(p->Hkv),
-                 static_cast<unsigned>(p->B));
+  kv.args.n_zblocks = cdiv(p->N, 128);
+  kv.args.grid_chunk = grid_chunk(1, 4ll * a.groups * p->M * D, a.causal != 0);
+  kv.grid = dim3(static_cast<unsigned>(static_cast<int64_t>(p->B) * p->Hkv * kv.args.n_zblocks));
   kv.bf16 = p->dtype == B200ATTN_BF16;
   kv.dropout = p->dropout_p > 0.f;
   kv.mode = MODE_KV;
@@ -103,8 +105,9 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
   qq.args.out1 = p->dq.ptr;
   qq.args.out1_sb = p->dq.stride[0]; qq.args.out1_sh = p->dq.stride[1]; qq.args.out1_sr = p->dq.stride[2];
   qq.args.out2 = nullptr;
-  qq.grid = dim3(static_cast<unsigned>(cdiv(p->M, 128)), static_cast<unsigned>(p->Hq),
-                 static_cast<unsigned>(p->B));
+  qq.args.n_zblocks = cdiv(p->M, 128);
+  qq.args.grid_chunk = grid_chunk(a.groups, 4ll * p->N * D, a.causal != 0);
+  qq.grid = dim3(static_cast<unsigned>(static_cast<int64_t>(p->B) * p->Hq * qq.args.n_zblocks));
   qq.bf16 = kv.bf16;
   qq.dropout = kv.dropout;
   qq.mode = MODE_Q;
@@ -135,8 +138,9 @@ static int run_total(const b200attn_total_params* p, float2* stats, cudaStream_t
   a.drop = make_dropout_ctx(0.f, 0, 0);
   a.status = p->status;
   L.args = a;
-  L.grid = dim3(static_cast<unsigned>(cdiv(p->N, 128)), static_cast<unsigned>(p->Hq),
-                static_cast<unsigned>(p->B));
+  L.args.n_zblocks = cdiv(p->N, 128);
+  L.args.grid_chunk = grid_chunk(1, 2ll * p->M * D, a.causal != 0);
+  L.grid = dim3(static_cast<unsigned>(static_cast<int64_t>(p->B) * p->Hq * L.args.n_zblocks));
   L.bf16 = p->dtype == B200ATTN_BF16;
   L.dropout = false;
   L.mode = MODE_TOTAL;

@@ -41,6 +41,7 @@ struct BwdArgs {
   const float2* stats;  // [B, Hq, Mpad] (lse*log2e, delta)
   float* tot;           // MODE_TOTAL: [B, Hq, N]
   int B, Hq, Hkv, M, N, Mpad, groups, causal;
+  int n_zblocks, grid_chunk;  // grid order, see decode_block()
   float sm_scale, qk_scale;
   DropoutCtx drop;
   int32_t* status;
@@ -90,26 +91,29 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int b = blockIdx.z;
   const int P_SEQ = args.N - args.M;
 
   // Row block, the heads it loops over and its column range [col_lo, col_hi) in steps of 64.
   int r0, h_first, n_heads, hk, col_lo, col_hi;
+  const int grid_heads = MODE == MODE_KV ? args.Hkv : args.Hq;
+  const BlockCoord bc = decode_block(blockIdx.x, args.B * grid_heads, args.n_zblocks, args.grid_chunk);
+  const int b = bc.bh / grid_heads;
+  const int grid_h = bc.bh % grid_heads;
   if constexpr (MODE == MODE_Q) {
-    r0 = (gridDim.x - 1 - blockIdx.x) * 128;  // longest (causal) blocks first
-    h_first = blockIdx.y;
+    r0 = (args.n_zblocks - 1 - bc.z) * 128;  // longest (causal) blocks first
+    h_first = grid_h;
     n_heads = 1;
     hk = h_first / args.groups;
     col_lo = 0;
     col_hi = args.causal ? min(args.N, max(0, P_SEQ + r0 + 128)) : args.N;
   } else {
-    r0 = blockIdx.x * 128;                    // small n0 = most visible queries = longest first
+    r0 = bc.z * 128;                          // small n0 = most visible queries = longest first
     if constexpr (MODE == MODE_KV) {
-      hk = blockIdx.y;
+      hk = grid_h;
       h_first = hk * args.groups;
       n_heads = args.groups;
     } else {
-      h_first = blockIdx.y;
+      h_first = grid_h;
       n_heads = 1;
       hk = h_first / args.groups;
     }

@@ -122,6 +122,34 @@ __device__ __forceinline__ float2 unpack2(uint32_t u) {
   }
 }
 
+// 1-D grid order. Blocks are numbered so that (batch, head) pairs are visited in chunks of `chunk`
+// pairs; inside a chunk the row-block index z is the slow coordinate. With z sorted from the
+// longest block to the shortest this dispatches long (causal) blocks first, while a chunk's K/V
+// (or Q/dO) working set stays small enough to live in L2.
+struct BlockCoord { int bh, z; };
+__device__ __forceinline__ BlockCoord decode_block(int id, int BH, int n_z, int chunk) {
+  const int per_chunk = chunk * n_z;
+  const int full = BH / chunk;
+  int c = id / per_chunk;
+  int width = chunk;
+  if (c >= full) { c = full; width = BH - full * chunk; }
+  const int rem = id - c * per_chunk;
+  BlockCoord out;
+  out.z = rem / width;
+  out.bh = c * chunk + rem - out.z * width;
+  return out;
+}
+// Number of (batch, head) pairs per chunk: all query heads of as many KV heads as fit `budget`
+// bytes of streamed operand per KV head (`bytes_per_kv_head`), at least one KV head.
+__host__ inline int grid_chunk(int groups, int64_t bytes_per_kv_head, bool causal) {
+  if (!causal) return groups;
+  const int64_t budget = 96ll << 20;
+  int64_t n = budget / (bytes_per_kv_head > 0 ? bytes_per_kv_head : 1);
+  if (n < 1) n = 1;
+  if (n > 4096) n = 4096;
+  return static_cast<int>(n) * groups;
+}
+
 // Status codes written to the optional device status word.
 enum : int32_t {
   ST_OK = 0,

@@ -57,8 +57,8 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
     set_error("fwd: dropout_p must be in [0, 1)");
     return B200ATTN_EINVAL;
   }
-  if (static_cast<int64_t>(p->B) > 65535 || static_cast<int64_t>(p->Hq) > 65535) {
-    set_error("fwd: B and Hq are limited to 65535");
+  if (static_cast<int64_t>(p->B) * p->Hq * cdiv(p->M, 256) > 2147483647ll) {
+    set_error("fwd: B * Hq * ceil(M / 256) exceeds the grid limit");
     return B200ATTN_EINVAL;
   }
 
@@ -92,8 +92,9 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
   a.qk_scale = p->sm_scale * 1.4426950408889634f;
   a.drop = make_dropout_ctx(p->dropout_p, p->seed, p->offset);
   a.status = p->status;
-  L.grid = dim3(static_cast<unsigned>(cdiv(p->M, 256)), static_cast<unsigned>(p->Hq),
-                static_cast<unsigned>(p->B));
+  a.n_zblocks = cdiv(p->M, 256);
+  a.grid_chunk = grid_chunk(a.groups, 4ll * p->N * p->D, a.causal != 0);
+  L.grid = dim3(static_cast<unsigned>(static_cast<int64_t>(p->B) * p->Hq * a.n_zblocks));
   L.bf16 = p->dtype == B200ATTN_BF16;
   L.dropout = p->dropout_p > 0.f;
   L.stream = static_cast<cudaStream_t>(stream);
@@ -171,8 +172,7 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
   }
   const int n_blocks = cdiv(p->N, 128);
   const int S = p->num_splits < n_blocks ? p->num_splits : n_blocks;
-  if (static_cast<int64_t>(cdiv(p->M, 256)) * p->num_splits > 2147483647ll || p->B > 65535 ||
-      p->Hq > 65535) {
+  if (static_cast<int64_t>(p->B) * p->Hq * cdiv(p->M, 256) * p->num_splits > 2147483647ll) {
     set_error("fwd_splitkv: grid too large");
     return B200ATTN_EINVAL;
   }
@@ -211,8 +211,9 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
   a.qk_scale = p->sm_scale * 1.4426950408889634f;
   a.drop = make_dropout_ctx(0.f, 0, 0);
   a.status = p->status;
-  L.grid = dim3(static_cast<unsigned>(cdiv(p->M, 256) * p->num_splits), static_cast<unsigned>(p->Hq),
-                static_cast<unsigned>(p->B));
+  a.n_zblocks = cdiv(p->M, 256) * p->num_splits;
+  a.grid_chunk = grid_chunk(a.groups, 4ll * p->N * p->D, a.causal != 0);
+  L.grid = dim3(static_cast<unsigned>(static_cast<int64_t>(p->B) * p->Hq * a.n_zblocks));
   L.bf16 = p->dtype == B200ATTN_BF16;
   L.dropout = false;
   L.stream = static_cast<cudaStream_t>(stream_);

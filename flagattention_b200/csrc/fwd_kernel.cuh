@@ -5,7 +5,8 @@
 //   warps 0-3  : softmax + epilogue for query tile 0 (thread r <-> row r, TMEM lane r)
 //   warps 4-7  : softmax + epilogue for query tile 1
 //   warp 8     : tcgen05.mma issuer (one elected lane)
-//   warp 9     : TMA producer (one elected lane)
+//   warp 9     : TMA producer (one elected lane); warps 10-11 idle (they complete the third
+//                warpgroup so registers can be moved to the softmax groups)
 // TMEM (512 columns): S0 | S1 (128 fp32 columns each, P aliases the first 64 columns of its S
 // as packed 16-bit pairs) and O0 | O1 (D fp32 columns each).
 // The two tiles ping-pong: while one tile's softmax runs on the CUDA cores the tensor core
@@ -44,6 +45,7 @@ struct FwdArgs {
   float* lse;
   int64_t o_stride_b, o_stride_h, o_stride_m, o_stride_split;
   int64_t lse_stride_b, lse_stride_h, lse_stride_split;
+  int n_zblocks, grid_chunk;        // grid order, see decode_block()
   int num_splits, tiles_per_split;  // split-KV: CTA `split` visits K/V tiles [split*tps, (split+1)*tps)
   int B, Hq, Hkv, M, N, groups;
   int causal, o_fp32;
@@ -70,7 +72,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 static constexpr float RESCALE_THRESHOLD = 8.0f;
 
 template <int D, bool BF16, bool DROPOUT>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmV, const FwdArgs args) {
   using Cfg = TileCfg<D>;
@@ -91,18 +93,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   uint64_t* v_full = k_empty + STAGES;      // [STAGES]
   uint64_t* v_empty = v_full + STAGES;      // [STAGES]
   uint64_t* s_full = v_empty + STAGES;      // [2]
-  uint64_t* p_full = s_full + 2;            // [2]
-  uint64_t* o_full = p_full + 2;            // [2]
+  uint64_t* p_half = s_full + 2;            // [2 tiles][2 halves]
+  uint64_t* o_full = p_half + 4;            // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int split = blockIdx.x % args.num_splits;
-  const int m_blk = gridDim.x / args.num_splits - 1 - blockIdx.x / args.num_splits;  // longest (causal) row blocks first
+  const BlockCoord bc = decode_block(blockIdx.x, args.B * args.Hq, args.n_zblocks, args.grid_chunk);
+  const int split = bc.z % args.num_splits;
+  const int m_blk = args.n_zblocks / args.num_splits - 1 - bc.z / args.num_splits;  // longest first
   const int j0 = split * args.tiles_per_split;  // first K/V tile of this CTA
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
+  const int h = bc.bh % args.Hq;
+  const int b = bc.bh / args.Hq;
   const int hk = h / args.groups;
   const int m0 = m_blk * 2 * BLOCK;
   const int P_SEQ = args.N - args.M;
@@ -130,7 +133,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_full[t], 128);
+      mbar_init(&p_half[2 * t], 128);
+      mbar_init(&p_half[2 * t + 1], 128);
       mbar_init(&o_full[t], 1);
     }
     *abort_flag = 0;
@@ -162,8 +166,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
   };
 
-  if (warp == 9) {
+  if (warp >= 10) {
+    reg_dealloc<80>();
+  } else if (warp == 9) {
     // ------------------------------------------------------------ TMA producer
+    reg_dealloc<80>();
     if (lane == 0 && n_max > 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
@@ -193,6 +200,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     __syncwarp();
   } else if (warp == 8) {
     // ------------------------------------------------------------- MMA issuer
+    reg_dealloc<80>();
     if (lane == 0 && n_max > 0) {
       constexpr uint32_t IDESC_QK = make_idesc(BF16, 128, BLOCK, false, false);
       constexpr uint32_t IDESC_PV = make_idesc(BF16, 128, D, false, true);
@@ -210,9 +218,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                  s > 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int t, int st, bool acc) {
+      auto issue_pv = [&](int t, int st, bool acc, int half) {
 #pragma unroll
-        for (int s = 0; s < BLOCK / 16; ++s) {
+        for (int s = half * (BLOCK / 32); s < (half + 1) * (BLOCK / 32); ++s) {
           mma_ts(tmem_base + 2 * BLOCK + t * D, tmem_base + t * BLOCK + s * 8,
                  smem_desc(Cfg::MNMAJOR_DESC, v_addr + st * Cfg::TILE_BYTES + s * 16 * Cfg::ROW_BYTES),
                  IDESC_PV, (acc || s > 0) ? 1u : 0u);
@@ -238,9 +246,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         for (int t = 0; t < 2; ++t) {
           if (j >= n_tiles[t]) continue;
-          if (!wait(&p_full[t], j & 1)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+          if (!wait(&p_half[2 * t], j & 1)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
           tc_fence_after();
-          issue_pv(t, st, j > 0);
+          issue_pv(t, st, j > 0, 0);
+          if (!wait(&p_half[2 * t + 1], j & 1)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+          tc_fence_after();
+          issue_pv(t, st, j > 0, 1);
           if (j + 1 < n_tiles[t]) {
             issue_qk(t, st_next);
             tc_commit(&s_full[t]);
@@ -256,6 +267,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     __syncwarp();
   } else {
     // ------------------------------------------------- softmax + epilogue warps
+    reg_alloc<208>();
     const int t = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const int m_glob = m0 + t * BLOCK + row;
@@ -336,30 +348,33 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const float m_eff = (m_run == -INFINITY) ? 0.f : m_run;
       const float neg_ms = -m_eff * qk_scale;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      // P goes back to TMEM in two halves of 64 keys so that the P V product can start on the
+      // first half while the second is still being exponentiated.
 #pragma unroll
-      for (int i = 0; i < 128; i += 4) {
-        float p0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), qk_scale, neg_ms));
-        float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_ms));
-        float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, neg_ms));
-        float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, neg_ms));
-        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-        if constexpr (DROPOUT) {
-          const uint64_t ctr = ctr_row + static_cast<uint64_t>((j0 + j) * BLOCK + i);
-          if (!dropout_keep(args.drop, ctr + 0)) p0 = 0.f;
-          if (!dropout_keep(args.drop, ctr + 1)) p1 = 0.f;
-          if (!dropout_keep(args.drop, ctr + 2)) p2 = 0.f;
-          if (!dropout_keep(args.drop, ctr + 3)) p3 = 0.f;
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int i = half * 64; i < half * 64 + 64; i += 4) {
+          float p0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), qk_scale, neg_ms));
+          float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_ms));
+          float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, neg_ms));
+          float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, neg_ms));
+          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          if constexpr (DROPOUT) {
+            const uint64_t ctr = ctr_row + static_cast<uint64_t>((j0 + j) * BLOCK + i);
+            if (!dropout_keep(args.drop, ctr + 0)) p0 = 0.f;
+            if (!dropout_keep(args.drop, ctr + 1)) p1 = 0.f;
+            if (!dropout_keep(args.drop, ctr + 2)) p2 = 0.f;
+            if (!dropout_keep(args.drop, ctr + 3)) p3 = 0.f;
+          }
+          s[i / 2 + 0] = pack2<BF16>(p0, p1);
+          s[i / 2 + 1] = pack2<BF16>(p2, p3);
         }
-        s[i / 2 + 0] = pack2<BF16>(p0, p1);
-        s[i / 2 + 1] = pack2<BF16>(p2, p3);
+        tmem_st32(tmem_s + half * 32, s + half * 32);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_half[2 * t + half]);
       }
       l_run += (sum0 + sum1) + (sum2 + sum3);
-
-      tmem_st32(tmem_s + 0, s + 0);
-      tmem_st32(tmem_s + 32, s + 32);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&p_full[t]);
     }
 
     // ------------------------------------------------------------- epilogue

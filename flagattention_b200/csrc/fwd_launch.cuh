@@ -24,7 +24,7 @@ int launch_fwd_variant(const FwdLaunch& L) {
     B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
-  kernel<<<L.grid, 320, smem, L.stream>>>(L.tmQ, L.tmK, L.tmV, L.args);
+  kernel<<<L.grid, 384, smem, L.stream>>>(L.tmQ, L.tmK, L.tmV, L.args);
   B200ATTN_CUDA_OK(cudaGetLastError());
   return B200ATTN_OK;
 }

@@ -227,6 +227,16 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+// Re-partition the register file between warpgroups (all four warps of a group must execute it).
+template <uint32_t N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <uint32_t N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ------------------------------------------------------ descriptor encoding
 // Shared-memory matrix descriptor (tcgen05): start address, leading/stride byte
 // offsets (all >> 4), descriptor version 1 at bit 46, swizzle mode at bits 61..63.
