@@ -286,6 +286,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling runs)")
+    ap.add_argument("--shard", default="auto", choices=["auto", "replicate", "heads", "ring"],
+                    help="N>1: replicate = every rank runs the whole per-GPU workload (weak scaling, "
+                         "default for training configs); heads = the workload's (batch x KV-group) units "
+                         "are split over the ranks (strong scaling, default for the 32k config); ring = "
+                         "ring-KV sequence parallel forward over NCCL (32k config only)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.batch > 0:
@@ -301,6 +306,20 @@ def main():
                    "l2_policy": "inputs+outputs per step exceed the 126 MB L2 (no flush needed)"}
     metric = "flash_attention fwd+bwd TFLOPS (bf16 causal D=128)" if args.config == DEFAULT_CONFIG \
         else f"flash_attention {cfg['mode']} TFLOPS ({args.config})"
+
+    shard_mode = args.shard
+    if shard_mode == "auto":
+        shard_mode = "heads" if (args.config == "c5_long_context_fwd" and world > 1) else "replicate"
+    if world == 1:
+        shard_mode = "replicate"
+    if shard_mode == "ring" and (cfg["mode"] != "fwd" or not cfg["causal"]):
+        raise SystemExit("--shard ring is the causal forward-only sequence-parallel mode")
+    scaling = "weak" if shard_mode == "replicate" else "strong"
+    config_desc["sharding"] = {
+        "replicate": "every rank runs the full workload on its own seeded inputs, no collective",
+        "heads": "the workload's (batch x KV-head-group) units are split over the ranks, no collective",
+        "ring": "sequence split zig-zag over the ranks, K/V shards rotated with NCCL send/recv",
+    }[shard_mode]
 
     if args.impl == "reference":
         # The reference's own CPU implementation of the path (its PyTorch attention, restated in
@@ -353,21 +372,40 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    q, k, v, do = make_inputs(cfg, device, seed=1000 + rank)
+    q, k, v, do = make_inputs(cfg, device, seed=1000 + (rank if shard_mode == "replicate" else 0))
     K = args.steps
+    total_flops_per_step = step_flops(cfg) * (world if shard_mode == "replicate" else 1)
+    ring_step = None
+    if shard_mode == "heads":
+        from flagattention_b200 import sharding
+        my = sharding.shard(q, k, v, rank, world, do)
+        if len(my) != 1:
+            raise SystemExit("heads sharding expects each rank's units to lie in one batch")
+        q, k, v, do = (t.contiguous() for t in my[0])
+        cfg = dict(cfg, B=1, Hq=q.shape[1], Hkv=k.shape[1])
+    elif shard_mode == "ring":
+        from flagattention_b200 import ring
+        q, k, v = (ring.zigzag_shard(t, rank, world) for t in (q, k, v))
+
+        def ring_step():
+            return ring.ring_attention_forward(q, k, v)
 
     # ---- device-resident timing --------------------------------------------------------------
+    step = (lambda: ring_step()) if ring_step is not None else (lambda: run_step(cfg, q, k, v, do))
     for _ in range(warmup):
-        run_step(cfg, q, k, v, do)
+        step()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     barrier()
     if sampler:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if ring_step is not None:
+        ring.LAUNCHES = 0
     e0.record()
     for _ in range(K):
-        run_step(cfg, q, k, v, do)
+        step()
     e1.record()
+    ring_launches = ring.LAUNCHES if ring_step is not None else 0
     barrier()
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler else None
@@ -381,7 +419,7 @@ def main():
             dist.destroy_process_group()
         return
     host_in = [t.cpu().pin_memory() for t in (q, k, v, do)]
-    outs = run_step(cfg, q, k, v, do)
+    outs = step()
     host_out = [torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory() for t in outs]
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = sum(t.numel() * t.element_size() for t in host_out)
@@ -390,7 +428,7 @@ def main():
     def e2e_step():
         for d, h in zip(dev_in, host_in):
             d.copy_(h, non_blocking=True)
-        res = run_step(cfg, *dev_in)
+        res = ring.ring_attention_forward(*dev_in[:3]) if ring_step is not None else run_step(cfg, *dev_in)
         for h, d in zip(host_out, res):
             h.copy_(d, non_blocking=True)
 
@@ -414,28 +452,30 @@ def main():
     result = None
     if rank == 0:
         peaks, peak_src = load_peaks()
-        kern_ms = time_kernels(cfg, q, k, v, do)
-        f_fwd = fwd_flops(cfg)
+        kcfg = dict(cfg, M=q.shape[2], N=k.shape[2])   # ring mode: the rank-local problem
+        kern_ms = time_kernels(kcfg, q, k, v, do)
+        f_fwd = fwd_flops(kcfg)
         # Algorithmic FLOPs per launch: forward 2 GEMMs; dK/dV kernel 4 of the backward's 5 GEMMs
         # (S, dP, dV, dK); dQ kernel 1 (its S and dP are recomputation and not counted).
         alg = {"fwd_kernel": f_fwd, "bwd_kernel<kv>": 2.0 * f_fwd, "bwd_kernel<q>": 0.5 * f_fwd}
         dominant = max((n for n in kern_ms if n in alg), key=lambda n: kern_ms[n])
         achieved = alg[dominant] / (kern_ms[dominant] * 1e-3) * 1e-12
         peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
-        value = step_flops(cfg) * K * world / (ms_total * 1e-3) * 1e-12
-        e2e_value = step_flops(cfg) * K * world / (ms_e2e_total * 1e-3) * 1e-12
+        value = total_flops_per_step * K / (ms_total * 1e-3) * 1e-12
+        e2e_value = total_flops_per_step * K / (ms_e2e_total * 1e-3) * 1e-12
         result = {
             "metric": metric, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": K,
-            "warmup": warmup, "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "bf16" if cfg["dtype"] == "bfloat16" else "fp16",
             "data": "synthetic", "config": config_desc,
-            "per_gpu_tflops": value / world, "tokens_per_s": cfg["B"] * cfg["M"] * K * world / (ms_total * 1e-3),
+            "per_gpu_tflops": value / world, "tokens_per_s": CONFIGS[args.config]["B"] * cfg["M"] * K * (world if shard_mode == "replicate" else 1)
+            / (ms_total * 1e-3),
             "frac_of_spec_peak_2250": value / world / 2250.0,
             "frac_of_measured_burst_peak": value / world / float(peaks.get("bf16_tflops", 1590.0)),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_total / K},
-            "gpu_launches": kernels_per_step(cfg) * K,
+            "gpu_launches": kernels_per_step(cfg) * K if ring_step is None else ring_launches,
             "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_src} sustained bf16",
                          "traffic": (NCU_TRAFFIC_BYTES.get(args.config) or {}).get(dominant)

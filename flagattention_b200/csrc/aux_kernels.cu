@@ -132,6 +132,51 @@ static int launch_delta(const b200attn_tensor* o, int o_dtype, const b200attn_te
   return B200ATTN_OK;
 }
 
+// Log-sum-exp merge of two partial attention results over disjoint key sets:
+// lse = log(exp(lse_a) + exp(lse_b)), o = o_a * exp(lse_a - lse) + o_b * exp(lse_b - lse).
+// The accumulator is updated in place; a partial with lse = -inf (no visible key) leaves it
+// unchanged. Both sides are [heads, rows_per_head, D] fp32 arrays of which `rows` rows per head,
+// starting at row0, take part. One thread per 4 features; the threads of a row sit in one warp.
+__global__ void __launch_bounds__(256)
+merge_partial_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc, const float* __restrict__ o_part,
+                     const float* __restrict__ lse_part, int64_t heads, int rows, int D, int acc_rph,
+                     int acc_row0, int part_rph, int part_row0, int first) {
+  const int vec_per_row = D / 4;
+  const int64_t total = heads * rows * vec_per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t flat_row = i / vec_per_row;
+    const int vec = static_cast<int>(i - flat_row * vec_per_row);
+    const int64_t head = flat_row / rows;
+    const int r = static_cast<int>(flat_row - head * rows);
+    const int64_t ra = head * acc_rph + acc_row0 + r;
+    const int64_t rb = head * part_rph + part_row0 + r;
+    const float lb = lse_part[rb];
+    const float la = first ? -INFINITY : lse_acc[ra];
+    const float mx = fmaxf(la, lb);
+    float wa = 0.f, wb = 0.f, lse = -INFINITY;
+    if (mx != -INFINITY) {
+      const float ea = __expf(la - mx), eb = __expf(lb - mx);
+      const float inv = 1.0f / (ea + eb);
+      wa = ea * inv;
+      wb = eb * inv;
+      lse = mx + __logf(ea + eb);
+    }
+    float4* pa = reinterpret_cast<float4*>(o_acc + ra * D) + vec;
+    float4 a = first ? make_float4(0.f, 0.f, 0.f, 0.f) : *pa;
+    const float4 b = reinterpret_cast<const float4*>(o_part + rb * D)[vec];
+    a.x = a.x * wa + b.x * wb;
+    a.y = a.y * wa + b.y * wb;
+    a.z = a.z * wa + b.z * wb;
+    a.w = a.w * wa + b.w * wb;
+    *pa = a;
+    // All threads of a row are lanes of one warp and have read lse_acc[ra] above; after the warp
+    // re-converges the lane owning the row's last vector publishes the new value.
+    __syncwarp(__activemask());
+    if (vec == vec_per_row - 1) lse_acc[ra] = lse;
+  }
+}
+
 static int check_vec_tensor(const b200attn_tensor* t, int eb, const char* name) {
   if (t == nullptr || t->ptr == nullptr) {
     set_error("%s: null tensor", name);
@@ -195,4 +240,30 @@ extern "C" int b200attn_bwd_delta(const b200attn_tensor* o, int32_t o_dtype, con
       set_error("bwd_delta: head dimension %d not in {16, 32, 64, 128}", D);
       return B200ATTN_EINVAL;
   }
+}
+
+extern "C" int b200attn_merge_partial(float* o_acc, float* lse_acc, const float* o_part,
+                                      const float* lse_part, int64_t heads, int32_t rows, int32_t D,
+                                      int32_t acc_rows_per_head, int32_t acc_row0,
+                                      int32_t part_rows_per_head, int32_t part_row0, int32_t first,
+                                      void* stream) {
+  using namespace b200attn;
+  if (o_acc == nullptr || lse_acc == nullptr || o_part == nullptr || lse_part == nullptr || heads <= 0 ||
+      rows <= 0 || (D != 16 && D != 32 && D != 64 && D != 128) || acc_row0 < 0 || part_row0 < 0 ||
+      acc_row0 + rows > acc_rows_per_head || part_row0 + rows > part_rows_per_head) {
+    set_error("merge_partial: bad argument");
+    return B200ATTN_EINVAL;
+  }
+  if (reinterpret_cast<uintptr_t>(o_acc) % 16 != 0 || reinterpret_cast<uintptr_t>(o_part) % 16 != 0) {
+    set_error("merge_partial: o buffers must be 16-byte aligned");
+    return B200ATTN_EINVAL;
+  }
+  const int64_t total = heads * rows * (D / 4);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  merge_partial_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      o_acc, lse_acc, o_part, lse_part, heads, rows, D, acc_rows_per_head, acc_row0, part_rows_per_head,
+      part_row0, first ? 1 : 0);
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
 }

@@ -162,6 +162,18 @@ typedef struct {
 
 int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stream);
 
+/* Merge of two partial attention results over disjoint key sets, in place on the accumulator:
+ * lse = log(exp(lse_acc) + exp(lse_part)), o_acc = o_acc*exp(lse_acc-lse) + o_part*exp(lse_part-lse).
+ * Both sides are contiguous fp32 arrays [heads, rows_per_head, D] (o) and [heads, rows_per_head]
+ * (lse); `rows` rows per head starting at acc_row0 / part_row0 take part. `first` != 0 treats
+ * the accumulator rows as empty (they are overwritten). The algebra of `_fwd_combine_kv_splits`
+ * (split_kv.py:199-231), used by the ring-KV sequence-parallel mode where the partials arrive one
+ * ring step at a time. */
+int b200attn_merge_partial(float* o_acc, float* lse_acc, const float* o_part, const float* lse_part,
+                           int64_t heads, int32_t rows, int32_t D, int32_t acc_rows_per_head,
+                           int32_t acc_row0, int32_t part_rows_per_head, int32_t part_row0,
+                           int32_t first, void* stream);
+
 /* Diagnostics. */
 int b200attn_abi_version(void);
 const char* b200attn_last_error(void);
