@@ -33,6 +33,14 @@ namespace b200attn {
 
 enum BwdMode : int { MODE_KV = 0, MODE_Q = 1, MODE_TOTAL = 2 };
 
+#ifdef B200ATTN_TIMING
+// Developer build only: per-phase clock64() stamps of block 0 (softmax warp 0 and the MMA thread).
+#define B200ATTN_STAMP(who, idx) \
+  do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (idx) < 8192 && args.trace) args.trace[(who) * 8192 + (idx)] = clock64(); } while (0)
+#else
+#define B200ATTN_STAMP(who, idx) do {} while (0)
+#endif
+
 struct BwdArgs {
   void* out1;  // MODE_KV: dK, MODE_Q: dQ
   void* out2;  // MODE_KV: dV
@@ -45,6 +53,9 @@ struct BwdArgs {
   float sm_scale, qk_scale;
   DropoutCtx drop;
   int32_t* status;
+#ifdef B200ATTN_TIMING
+  long long* trace;
+#endif
 };
 
 template <int D, int MODE>
@@ -207,7 +218,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
     __syncwarp();
   } else if (warp == 8) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0 && T > 0) {
+    // The whole warp runs this loop with warp-uniform values; one elected lane issues each
+    // tcgen05 instruction (see mma_ss_w).
+    if (T > 0) {
       constexpr uint32_t IDESC_T = make_idesc(BF16, 128, STEP, false, false);
       constexpr uint32_t IDESC_ACC = make_idesc(BF16, 128, D, false, true);
       const uint32_t a_addr = smem_u32(sA);
@@ -215,17 +228,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       // T1 = A1 B1^T, T2 = A2 B2^T into buffer `buf` from ring stage `st`.
       auto issue_t = [&](int buf, int st) {
         const uint32_t t1 = tmem_base + BUF_BASE + buf * 128;
-        const uint32_t sb = b_addr + st * Sm::STAGE_BYTES;
+        const uint64_t da = smem_desc(Cfg::KMAJOR_DESC, a_addr);
+        const uint64_t db = smem_desc(Cfg::KMAJOR_DESC, b_addr + st * Sm::STAGE_BYTES);
 #pragma unroll
         for (int which = 0; which < Sm::N_A; ++which) {
 #pragma unroll
           for (int s = 0; s < D / 16; ++s) {
+            constexpr int dummy = 0; (void)dummy;
             const uint32_t a_off = which * Cfg::TILE_BYTES + (s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
                                    (s % Cfg::STEPS_PER_CHUNK) * 32;
             const uint32_t b_off = which * Sm::B_TILE_BYTES + (s / Cfg::STEPS_PER_CHUNK) * CHUNK_BYTES_B +
                                    (s % Cfg::STEPS_PER_CHUNK) * 32;
-            mma_ss(t1 + which * 64, smem_desc(Cfg::KMAJOR_DESC, a_addr + a_off),
-                   smem_desc(Cfg::KMAJOR_DESC, sb + b_off), IDESC_T, s > 0 ? 1u : 0u);
+            // offsets are multiples of 16 bytes and stay inside shared memory, so they add into
+            // the 14-bit address field without carrying out of it
+            mma_ss_w(t1 + which * 64, da + (a_off >> 4), db + (b_off >> 4), IDESC_T, s > 0 ? 1u : 0u);
           }
         }
       };
@@ -233,41 +249,50 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       auto issue_acc = [&](int acc, int buf, int src, int st, int tile, bool accumulate) {
         const uint32_t d = tmem_base + acc * D;
         const uint32_t a = tmem_base + BUF_BASE + buf * 128 + src * 64;
-        const uint32_t sb = b_addr + st * Sm::STAGE_BYTES + tile * Sm::B_TILE_BYTES;
+        const uint64_t db = smem_desc(MN_DESC_B, b_addr + st * Sm::STAGE_BYTES + tile * Sm::B_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < STEP / 16; ++s)
-          mma_ts(d, a + s * 8, smem_desc(MN_DESC_B, sb + s * 16 * Cfg::ROW_BYTES), IDESC_ACC,
-                 (accumulate || s > 0) ? 1u : 0u);
+          mma_ts_w(d, a + s * 8, db + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_ACC,
+                   (accumulate || s > 0) ? 1u : 0u);
       };
       bool ok = true;
       if (!wait(a_full, 0)) { fail(ST_WAIT_TMA); ok = false; }
       if (ok && !wait(&b_full[0], 0)) { fail(ST_WAIT_TMA); ok = false; }
+      ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
         issue_t(0, 0);
-        tc_commit(&t_full[0]);
+        tc_commit_w(&t_full[0]);
       }
       for (int i = 0; i < T && ok; ++i) {
         const int buf = i & 1;
         const int st = i % STAGES;
         if (i + 1 < T) {
           const int st_next = (i + 1) % STAGES;
-          if (!wait(&b_full[st_next], ((i + 1) / STAGES) & 1)) { fail(ST_WAIT_TMA); ok = false; break; }
+          B200ATTN_STAMP(1, 4 * i + 0);
+          const bool w = wait(&b_full[st_next], ((i + 1) / STAGES) & 1);
+          if (!__all_sync(0xffffffffu, w)) { fail(ST_WAIT_TMA); ok = false; break; }
           tc_fence_after();
+          B200ATTN_STAMP(1, 4 * i + 1);
           issue_t(buf ^ 1, st_next);
-          tc_commit(&t_full[buf ^ 1]);
+          tc_commit_w(&t_full[buf ^ 1]);
         }
-        if (!wait(&p_ready[buf], (i >> 1) & 1)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+        B200ATTN_STAMP(1, 4 * i + 2);
+        {
+          const bool w = wait(&p_ready[buf], (i >> 1) & 1);
+          if (!__all_sync(0xffffffffu, w)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+        }
         tc_fence_after();
+        B200ATTN_STAMP(1, 4 * i + 3);
         if constexpr (MODE == MODE_KV) {
           issue_acc(1, buf, 0, st, 1, i > 0);  // dV += P^T  dO
           issue_acc(0, buf, 1, st, 0, i > 0);  // dK += dS^T Q
         } else if constexpr (MODE == MODE_Q) {
           issue_acc(0, buf, 1, st, 0, i > 0);  // dQ += dS K
         }
-        tc_commit(&b_empty[st]);
+        tc_commit_w(&b_empty[st]);
       }
-      if (ok) tc_commit(acc_full);
+      if (ok) tc_commit_w(acc_full);
     }
     __syncwarp();
   } else {
@@ -296,11 +321,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       const int col0 = col_lo + (i - hh * steps_per_head) * STEP;
       const int h = h_first + hh;
       const uint32_t t1_addr = tmem_base + lane_base + BUF_BASE + wg * 128;
+      if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 0);
       {
         const bool w = wait(&t_full[wg], (i >> 1) & 1);
         if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
       }
       tc_fence_after();
+      if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 1);
       uint32_t t1[64];
       uint32_t t2[MODE == MODE_TOTAL ? 1 : 64];
       tmem_ld32(t1_addr, t1);
@@ -310,6 +337,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         tmem_ld32(t1_addr + 96, t2 + 32);
       }
       tmem_wait_ld();
+      if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 2);
 
       // Does this step cross the causal boundary for some row of the block?
       bool diag = false;
@@ -382,6 +410,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       }
       tc_fence_before();
       mbar_arrive(&p_ready[wg]);
+      if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 3);
     }
 
     // ------------------------------------------------------------- epilogue

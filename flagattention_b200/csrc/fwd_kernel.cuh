@@ -200,68 +200,77 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     __syncwarp();
   } else if (warp == 8) {
     // ------------------------------------------------------------- MMA issuer
+    // The whole warp runs this loop with warp-uniform values; one elected lane issues each
+    // tcgen05 instruction (see mma_ss_w).
     reg_dealloc<80>();
-    if (lane == 0 && n_max > 0) {
+    if (n_max > 0) {
       constexpr uint32_t IDESC_QK = make_idesc(BF16, 128, BLOCK, false, false);
       constexpr uint32_t IDESC_PV = make_idesc(BF16, 128, D, false, true);
       const uint32_t q_addr = smem_u32(sQ);
       const uint32_t k_addr = smem_u32(sK);
       const uint32_t v_addr = smem_u32(sV);
       auto issue_qk = [&](int t, int st) {
+        const uint64_t dq = smem_desc(Cfg::KMAJOR_DESC, q_addr + t * Cfg::TILE_BYTES);
+        const uint64_t dk = smem_desc(Cfg::KMAJOR_DESC, k_addr + st * Cfg::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < D / 16; ++s) {
-          const uint32_t off = (s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
-                               (s % Cfg::STEPS_PER_CHUNK) * 32;
-          mma_ss(tmem_base + t * BLOCK,
-                 smem_desc(Cfg::KMAJOR_DESC, q_addr + t * Cfg::TILE_BYTES + off),
-                 smem_desc(Cfg::KMAJOR_DESC, k_addr + st * Cfg::TILE_BYTES + off), IDESC_QK,
-                 s > 0 ? 1u : 0u);
+          // offsets are multiples of 16 bytes inside shared memory: they add into the 14-bit
+          // address field of the descriptor without carrying out of it
+          const uint32_t off = ((s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
+                                (s % Cfg::STEPS_PER_CHUNK) * 32) >> 4;
+          mma_ss_w(tmem_base + t * BLOCK, dq + off, dk + off, IDESC_QK, s > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int t, int st, bool acc, int half) {
+        const uint64_t dv = smem_desc(Cfg::MNMAJOR_DESC, v_addr + st * Cfg::TILE_BYTES);
 #pragma unroll
         for (int s = half * (BLOCK / 32); s < (half + 1) * (BLOCK / 32); ++s) {
-          mma_ts(tmem_base + 2 * BLOCK + t * D, tmem_base + t * BLOCK + s * 8,
-                 smem_desc(Cfg::MNMAJOR_DESC, v_addr + st * Cfg::TILE_BYTES + s * 16 * Cfg::ROW_BYTES),
-                 IDESC_PV, (acc || s > 0) ? 1u : 0u);
+          mma_ts_w(tmem_base + 2 * BLOCK + t * D, tmem_base + t * BLOCK + s * 8,
+                   dv + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_PV, (acc || s > 0) ? 1u : 0u);
         }
+      };
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, int32_t code) -> bool {
+        const bool w = wait(bar, parity);
+        if (__all_sync(0xffffffffu, w)) return true;
+        fail(code);
+        return false;
       };
       bool ok = true;
       // Prologue: S_t = Q_t K_0^T for both tiles.
-      if (!wait(&k_full[0], 0)) { fail(ST_WAIT_TMA); ok = false; }
+      ok = wait_all(&k_full[0], 0, ST_WAIT_TMA);
       for (int t = 0; t < 2 && ok; ++t) {
         if (n_tiles[t] == 0) continue;
-        if (!wait(&q_full[t], 0)) { fail(ST_WAIT_TMA); ok = false; break; }
+        if (!wait_all(&q_full[t], 0, ST_WAIT_TMA)) { ok = false; break; }
         tc_fence_after();
         issue_qk(t, 0);
-        tc_commit(&s_full[t]);
+        tc_commit_w(&s_full[t]);
       }
-      if (ok) tc_commit(&k_empty[0]);
+      if (ok) tc_commit_w(&k_empty[0]);
       for (int j = 0; j < n_max && ok; ++j) {
         const int st = j % STAGES;
         const int st_next = (j + 1) % STAGES;
-        if (!wait(&v_full[st], (j / STAGES) & 1)) { fail(ST_WAIT_TMA); break; }
+        if (!wait_all(&v_full[st], (j / STAGES) & 1, ST_WAIT_TMA)) break;
         if (j + 1 < n_max) {
-          if (!wait(&k_full[st_next], ((j + 1) / STAGES) & 1)) { fail(ST_WAIT_TMA); break; }
+          if (!wait_all(&k_full[st_next], ((j + 1) / STAGES) & 1, ST_WAIT_TMA)) break;
         }
         for (int t = 0; t < 2; ++t) {
           if (j >= n_tiles[t]) continue;
-          if (!wait(&p_half[2 * t], j & 1)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+          if (!wait_all(&p_half[2 * t], j & 1, ST_WAIT_SOFTMAX)) { ok = false; break; }
           tc_fence_after();
           issue_pv(t, st, j > 0, 0);
-          if (!wait(&p_half[2 * t + 1], j & 1)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+          if (!wait_all(&p_half[2 * t + 1], j & 1, ST_WAIT_SOFTMAX)) { ok = false; break; }
           tc_fence_after();
           issue_pv(t, st, j > 0, 1);
           if (j + 1 < n_tiles[t]) {
             issue_qk(t, st_next);
-            tc_commit(&s_full[t]);
+            tc_commit_w(&s_full[t]);
           } else {
-            tc_commit(&o_full[t]);
+            tc_commit_w(&o_full[t]);
           }
         }
         if (!ok) break;
-        tc_commit(&v_empty[st]);
-        if (j + 1 < n_max) tc_commit(&k_empty[st_next]);
+        tc_commit_w(&v_empty[st]);
+        if (j + 1 < n_max) tc_commit_w(&k_empty[st_next]);
       }
     }
     __syncwarp();
