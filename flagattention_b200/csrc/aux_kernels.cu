@@ -80,34 +80,39 @@ delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __
   if (row_id < total && (lane % LANES) == 0) delta[row_id] = acc;
 }
 
-// stats[b, h, m] = (lse * log2(e), delta) for m < M and (+inf, 0) for the padding rows m in
-// [M, Mpad). Rows without any visible key (lse = -inf) also get +inf so that every probability
-// recomputed against them is exactly 0.
+// Per-query statistics for the backward / total-attention kernels, two queries per float4:
+// stats4[b, h, m/2] = (-lse[m]*log2e, -lse[m+1]*log2e, -delta[m], -delta[m+1]); the padding rows
+// m in [M, Mpad) get (-inf, 0). Rows without any visible key (lse = -inf) also get -inf, so that
+// every probability recomputed against them, exp2(s*c + (-inf)), is exactly 0.
 __global__ void __launch_bounds__(256)
-stats_kernel(const float* __restrict__ lse, const float* __restrict__ delta, float2* __restrict__ stats,
+stats_kernel(const float* __restrict__ lse, const float* __restrict__ delta, float4* __restrict__ stats,
              int64_t BH, int M, int Mpad) {
-  const int64_t total = BH * Mpad;
+  const int half = Mpad / 2;
+  const int64_t total = BH * half;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t bh = i / Mpad;
-    const int m = static_cast<int>(i - bh * Mpad);
-    float2 out = make_float2(INFINITY, 0.f);
-    if (m < M) {
-      const float l = lse[bh * M + m];
-      out.x = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
-      out.y = delta != nullptr ? delta[bh * M + m] : 0.f;
+    const int64_t bh = i / half;
+    const int m = static_cast<int>(i - bh * half) * 2;
+    float nl[2] = {-INFINITY, -INFINITY}, nd[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      if (m + j < M) {
+        const float l = lse[bh * M + m + j];
+        nl[j] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
+        nd[j] = delta != nullptr ? -delta[bh * M + m + j] : 0.f;
+      }
     }
-    stats[i] = out;
+    stats[i] = make_float4(nl[0], nl[1], nd[0], nd[1]);
   }
 }
 
 int launch_stats(const float* lse, const float* delta, float2* stats, int B, int H, int M, int Mpad,
                  cudaStream_t stream) {
-  const int64_t total = static_cast<int64_t>(B) * H * Mpad;
+  const int64_t total = static_cast<int64_t>(B) * H * (Mpad / 2);
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  stats_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(lse, delta, stats,
-                                                                  static_cast<int64_t>(B) * H, M, Mpad);
+  stats_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      lse, delta, reinterpret_cast<float4*>(stats), static_cast<int64_t>(B) * H, M, Mpad);
   B200ATTN_CUDA_OK(cudaGetLastError());
   return B200ATTN_OK;
 }
