@@ -21,9 +21,10 @@
 // (T1, T2) buffers of 64+64 fp32 columns; P / dS overwrite the head of T1 / T2 as packed 16-bit
 // pairs and are consumed from TMEM as the A operand of the accumulating MMAs.
 //
-// Per-column statistics come from a padded scratch array stats[b, h, m] = (lse*log2e, delta),
-// padded to a multiple of 128 queries with (+inf, 0) so that padded and key-less queries contribute
-// exactly zero.
+// Per-query statistics come from a padded scratch array holding, per pair of queries, the float4
+// (-lse[m]*log2e, -lse[m+1]*log2e, -delta[m], -delta[m+1]); it is padded to a multiple of 128
+// queries with (-inf, 0) so that padded and key-less queries contribute exactly zero. The pair
+// layout feeds the packed f32x2 arithmetic of the recompute loop directly.
 #pragma once
 #include "common.cuh"
 #include "fwd_kernel.cuh"
@@ -46,7 +47,7 @@ struct BwdArgs {
   void* out2;  // MODE_KV: dV
   int64_t out1_sb, out1_sh, out1_sr;
   int64_t out2_sb, out2_sh, out2_sr;
-  const float2* stats;  // [B, Hq, Mpad] (lse*log2e, delta)
+  const float2* stats;  // [B, Hq, Mpad/2] float4 pairs, see above
   float* tot;           // MODE_TOTAL: [B, Hq, N]
   int B, Hq, Hkv, M, N, Mpad, groups, causal;
   int n_zblocks, grid_chunk;  // grid order, see decode_block()
@@ -302,16 +303,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
     const int row = r0 + row_local;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const float qk_scale = args.qk_scale;
-    float row_lse2 = 0.f, row_delta = 0.f;
+    float row_nlse = -INFINITY, row_ndelta = 0.f;   // MODE_Q: this row's -lse*log2e and -delta
     if constexpr (MODE == MODE_Q) {
       if (row < args.Mpad) {
-        const float2 st = args.stats[(static_cast<int64_t>(b) * args.Hq + h_first) * args.Mpad + row];
-        row_lse2 = st.x;
-        row_delta = st.y;
-      } else {
-        row_lse2 = INFINITY;
+        const float* st = reinterpret_cast<const float*>(args.stats) +
+                          ((static_cast<int64_t>(b) * args.Hq + h_first) * args.Mpad + (row & ~1)) * 2;
+        row_nlse = st[row & 1];
+        row_ndelta = st[2 + (row & 1)];
       }
     }
+    const uint64_t scale2 = f2_pack(qk_scale, qk_scale);
     float tot_sum = 0.f;
     bool ok = true;
 
@@ -361,16 +362,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
 
 #pragma unroll
       for (int c = 0; c < STEP; c += 2) {
-        float lse_a, lse_b, del_a, del_b;
+        uint64_t nlse2, ndel2;
         if constexpr (MODE == MODE_Q) {
-          lse_a = lse_b = row_lse2;
-          del_a = del_b = row_delta;
+          nlse2 = f2_pack(row_nlse, row_nlse);
+          ndel2 = f2_pack(row_ndelta, row_ndelta);
         } else {
           const float4 sv = stats4[c >> 1];
-          lse_a = sv.x; del_a = sv.y; lse_b = sv.z; del_b = sv.w;
+          nlse2 = f2_pack(sv.x, sv.y);
+          ndel2 = f2_pack(sv.z, sv.w);
         }
-        float p_a = fast_exp2(fmaf(__uint_as_float(t1[c]), qk_scale, -lse_a));
-        float p_b = fast_exp2(fmaf(__uint_as_float(t1[c + 1]), qk_scale, -lse_b));
+        // p = exp2(s * qk_scale - lse * log2e) for two columns at once
+        float x_a, x_b;
+        f2_unpack(f2_fma(f2_pack(__uint_as_float(t1[c]), __uint_as_float(t1[c + 1])), scale2, nlse2), x_a, x_b);
+        float p_a = fast_exp2(x_a);
+        float p_b = fast_exp2(x_b);
         if (diag) {
           bool vis_a, vis_b;
           if constexpr (MODE == MODE_Q) {
@@ -397,8 +402,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
             dp_a = keep_a ? dp_a * args.drop.inv_keep : 0.f;
             dp_b = keep_b ? dp_b * args.drop.inv_keep : 0.f;
           }
-          const float ds_a = p_a * (dp_a - del_a);
-          const float ds_b = p_b * (dp_b - del_b);
+          // dS = P * (dP - delta)
+          float ds_a, ds_b;
+          f2_unpack(f2_mul(f2_pack(p_a, p_b), f2_add(f2_pack(dp_a, dp_b), ndel2)), ds_a, ds_b);
           t1[c >> 1] = pack2<BF16>(pd_a, pd_b);
           t2[c >> 1] = pack2<BF16>(ds_a, ds_b);
         }
