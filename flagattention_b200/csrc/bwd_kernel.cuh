@@ -18,8 +18,8 @@
 //
 // Roles: warps 0-3 and 4-7 are two softmax groups that alternate steps (thread r <-> row r), warp 8
 // issues tcgen05.mma, warp 9 drives TMA. TMEM: accumulators (D columns each) followed by two
-// (T1, T2) buffers of 64+64 fp32 columns; P / dS overwrite the head of T1 / T2 as packed 16-bit
-// pairs and are consumed from TMEM as the A operand of the accumulating MMAs.
+// (T1, T2) buffers of 64+64 fp32 columns; P / dS overwrite T1 as packed 16-bit pairs and are
+// consumed from TMEM as the A operand of the accumulating MMAs.
 //
 // Per-query statistics come from a padded scratch array holding, per pair of queries, the float4
 // (-lse[m]*log2e, -lse[m+1]*log2e, -delta[m], -delta[m+1]); it is padded to a multiple of 128
@@ -143,7 +143,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&t_full[i], 1);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&p_ready[i], 256);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -249,11 +249,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       // acc[which] += (P or dS from TMEM) x streamed tile `tile` of stage `st`, read MN-major.
       auto issue_acc = [&](int acc, int buf, int src, int st, int tile, bool accumulate) {
         const uint32_t d = tmem_base + acc * D;
-        const uint32_t a = tmem_base + BUF_BASE + buf * 128 + src * 64;
+        // Softmax group g leaves its 32 columns' P (8+8 packed columns) at T1[32g, 32g+16) and
+        // its dS at T1[32g+16, 32g+32): K-step s covers columns 16s..16s+15 of the step.
+        const uint32_t a = tmem_base + BUF_BASE + buf * 128 + src * 16;
         const uint64_t db = smem_desc(MN_DESC_B, b_addr + st * Sm::STAGE_BYTES + tile * Sm::B_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < STEP / 16; ++s)
-          mma_ts_w(d, a + s * 8, db + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_ACC,
+          mma_ts_w(d, a + (s >> 1) * 32 + (s & 1) * 8, db + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_ACC,
                    (accumulate || s > 0) ? 1u : 0u);
       };
       bool ok = true;
@@ -316,37 +318,38 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
     float tot_sum = 0.f;
     bool ok = true;
 
-    for (int i = wg; i < T; i += 2) {
+    // Both groups work on every step: group `wg` owns columns [32*wg, 32*wg + 32) of the step, which
+    // halves the latency between the T products and the accumulating products of a step.
+    constexpr int HALF = STEP / 2;
+    for (int i = 0; i < T; ++i) {
       const int st = i % STAGES;
+      const int buf = i & 1;
       const int hh = i / steps_per_head;
-      const int col0 = col_lo + (i - hh * steps_per_head) * STEP;
+      const int col0 = col_lo + (i - hh * steps_per_head) * STEP + wg * HALF;  // first column of this group
       const int h = h_first + hh;
-      const uint32_t t1_addr = tmem_base + lane_base + BUF_BASE + wg * 128;
+      const uint32_t t1_addr = tmem_base + lane_base + BUF_BASE + buf * 128;
       if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 0);
       {
-        const bool w = wait(&t_full[wg], (i >> 1) & 1);
+        const bool w = wait(&t_full[buf], (i >> 1) & 1);
         if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
       }
       tc_fence_after();
       if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 1);
-      uint32_t t1[64];
-      uint32_t t2[MODE == MODE_TOTAL ? 1 : 64];
-      tmem_ld32(t1_addr, t1);
-      tmem_ld32(t1_addr + 32, t1 + 32);
-      if constexpr (MODE != MODE_TOTAL) {
-        tmem_ld32(t1_addr + 64, t2);
-        tmem_ld32(t1_addr + 96, t2 + 32);
-      }
+      uint32_t t1[HALF];
+      uint32_t t2[MODE == MODE_TOTAL ? 1 : HALF];
+      tmem_ld32(t1_addr + wg * HALF, t1);
+      if constexpr (MODE != MODE_TOTAL) tmem_ld32(t1_addr + 64 + wg * HALF, t2);
       tmem_wait_ld();
       if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 2);
 
       // Does this step cross the causal boundary for some row of the block?
       bool diag = false;
       if (args.causal) {
-        if constexpr (MODE == MODE_Q) diag = col0 + STEP - 1 > r0 + P_SEQ;
+        if constexpr (MODE == MODE_Q) diag = col0 + HALF - 1 > r0 + P_SEQ;
         else diag = col0 + P_SEQ < r0 + 127;
       }
-      const float4* stats4 = reinterpret_cast<const float4*>(sB + st * Sm::STAGE_BYTES + Sm::N_B * Sm::B_TILE_BYTES);
+      const float4* stats4 = reinterpret_cast<const float4*>(sB + st * Sm::STAGE_BYTES + Sm::N_B * Sm::B_TILE_BYTES) +
+                             wg * (HALF / 2);
       uint64_t ctr0 = 0, ctr_step = 0;
       if constexpr (DROPOUT) {
         const uint64_t head_base = args.drop.offset +
@@ -361,7 +364,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       }
 
 #pragma unroll
-      for (int c = 0; c < STEP; c += 2) {
+      for (int c = 0; c < HALF; c += 2) {
         uint64_t nlse2, ndel2;
         if constexpr (MODE == MODE_Q) {
           nlse2 = f2_pack(row_nlse, row_nlse);
@@ -410,12 +413,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         }
       }
       if constexpr (MODE != MODE_TOTAL) {
-        if constexpr (MODE == MODE_KV) tmem_st32(t1_addr, t1);
-        tmem_st32(t1_addr + 64, t2);
+        // Outputs go over this group's own (already loaded) T1 columns only, so the two groups
+        // never touch each other's unread inputs.
+        if constexpr (MODE == MODE_KV) tmem_st16(t1_addr + wg * HALF, t1);
+        tmem_st16(t1_addr + wg * HALF + 16, t2);
         tmem_wait_st();
       }
       tc_fence_before();
-      mbar_arrive(&p_ready[wg]);
+      mbar_arrive(&p_ready[buf]);
       if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 3);
     }
 
