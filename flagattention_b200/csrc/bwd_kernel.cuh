@@ -350,19 +350,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       }
       const float4* stats4 = reinterpret_cast<const float4*>(sB + st * Sm::STAGE_BYTES + Sm::N_B * Sm::B_TILE_BYTES) +
                              wg * (HALF / 2);
-      uint64_t ctr0 = 0, ctr_step = 0;
-      if constexpr (DROPOUT) {
-        const uint64_t head_base = args.drop.offset +
-                                   (static_cast<uint64_t>(b) * args.Hq + h) * args.M * static_cast<uint64_t>(args.N);
-        if constexpr (MODE == MODE_Q) {
-          ctr0 = head_base + static_cast<uint64_t>(row) * args.N + col0;
-          ctr_step = 1;
-        } else {
-          ctr0 = head_base + static_cast<uint64_t>(col0) * args.N + row;
-          ctr_step = args.N;
-        }
-      }
-
 #pragma unroll
       for (int c = 0; c < HALF; c += 2) {
         uint64_t nlse2, ndel2;
@@ -398,8 +385,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           float dp_b = __uint_as_float(t2[c + 1]);
           float pd_a = p_a, pd_b = p_b;
           if constexpr (DROPOUT) {
-            const bool keep_a = dropout_keep(args.drop, ctr0 + ctr_step * c);
-            const bool keep_b = dropout_keep(args.drop, ctr0 + ctr_step * (c + 1));
+            const bool keep_a = (keep_bits >> c) & 1u;
+            const bool keep_b = (keep_bits >> (c + 1)) & 1u;
             pd_a = keep_a ? p_a : 0.f;
             pd_b = keep_b ? p_b : 0.f;
             dp_a = keep_a ? dp_a * args.drop.inv_keep : 0.f;

@@ -99,6 +99,40 @@ __device__ __forceinline__ bool dropout_keep(const DropoutCtx& c, uint64_t ctr) 
   return folded > c.keep_threshold;
 }
 
+// Keep decisions of 32 consecutive counters base, base+1, ..., base+31 as a bit mask (bit i = element
+// i is kept). The counter's high word is the same for all 32 unless the low word wraps inside the
+// run, which lets the compiler hoist the first Philox round's key mixing out of the loop.
+__device__ __forceinline__ uint32_t dropout_keep_word(const DropoutCtx& c, uint64_t base) {
+  const uint32_t lo0 = static_cast<uint32_t>(base);
+  uint32_t bits = 0u;
+  if (lo0 <= 0xffffffffu - 31u) {
+    const uint32_t hi = c.wide ? static_cast<uint32_t>(base >> 32) : 0u;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int32_t x = static_cast<int32_t>(philox6_word0(c.seed_lo, c.seed_hi, lo0 + i, hi));
+      bits |= ((x ^ (x >> 31)) > c.keep_threshold ? 1u : 0u) << i;
+    }
+  } else {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) bits |= (dropout_keep(c, base + i) ? 1u : 0u) << i;
+  }
+  return bits;
+}
+
+// Same for 32 counters base + i * stride (elements of one key column across consecutive queries).
+__device__ __forceinline__ uint32_t dropout_keep_word_strided(const DropoutCtx& c, uint64_t base,
+                                                              uint64_t stride) {
+  uint32_t bits = 0u;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const uint64_t ctr = base + stride * static_cast<uint64_t>(i);
+    const uint32_t hi = c.wide ? static_cast<uint32_t>(ctr >> 32) : 0u;
+    const int32_t x = static_cast<int32_t>(philox6_word0(c.seed_lo, c.seed_hi, static_cast<uint32_t>(ctr), hi));
+    bits |= ((x ^ (x >> 31)) > c.keep_threshold ? 1u : 0u) << i;
+  }
+  return bits;
+}
+
 // ------------------------------------------------------------ small helpers
 __host__ __device__ constexpr int cdiv(int a, int b) { return (a + b - 1) / b; }
 

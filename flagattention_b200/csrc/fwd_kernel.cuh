@@ -301,6 +301,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     bool ok = true;
 
     for (int j = 0; j < nt; ++j) {
+      // Dropout decisions of this row for the tile's 128 keys, generated before S is awaited so the
+      // integer work overlaps the tensor core instead of extending the softmax phase.
+      uint32_t keep_bits[DROPOUT ? 4 : 1];
+      if constexpr (DROPOUT) {
+        const uint64_t base = ctr_row + static_cast<uint64_t>((j0 + j) * BLOCK);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) keep_bits[w] = dropout_keep_word(args.drop, base + 32 * w);
+      }
       {
         const bool w = wait(&s_full[t], j & 1);
         if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
@@ -369,11 +377,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, neg_ms));
           sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
           if constexpr (DROPOUT) {
-            const uint64_t ctr = ctr_row + static_cast<uint64_t>((j0 + j) * BLOCK + i);
-            if (!dropout_keep(args.drop, ctr + 0)) p0 = 0.f;
-            if (!dropout_keep(args.drop, ctr + 1)) p1 = 0.f;
-            if (!dropout_keep(args.drop, ctr + 2)) p2 = 0.f;
-            if (!dropout_keep(args.drop, ctr + 3)) p3 = 0.f;
+            const uint32_t kb = keep_bits[i >> 5] >> (i & 31);
+            if (!(kb & 1u)) p0 = 0.f;
+            if (!(kb & 2u)) p1 = 0.f;
+            if (!(kb & 4u)) p2 = 0.f;
+            if (!(kb & 8u)) p3 = 0.f;
           }
           s[i / 2 + 0] = pack2<BF16>(p0, p1);
           s[i / 2 + 1] = pack2<BF16>(p2, p3);
