@@ -37,7 +37,7 @@ enum BwdMode : int { MODE_KV = 0, MODE_Q = 1, MODE_TOTAL = 2 };
 #ifdef B200ATTN_TIMING
 // Developer build only: per-phase clock64() stamps of block 0 (softmax warp 0 and the MMA thread).
 #define B200ATTN_STAMP(who, idx) \
-  do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (idx) < 8192 && args.trace) args.trace[(who) * 8192 + (idx)] = clock64(); } while (0)
+  do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (idx) < 8192 && args.trace) args.trace[(who) * 8192 + (idx)] = clock64(); __syncwarp(); } while (0)
 #else
 #define B200ATTN_STAMP(who, idx) do {} while (0)
 #endif
@@ -170,6 +170,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       if (mbar_try_wait(bar, parity)) return true;
       if ((++spins & 0xffu) == 0u) {
         if (*abort_flag) return false;
+        if (args.status != nullptr && *reinterpret_cast<volatile int32_t*>(args.status) != 0) return false;
         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
       }
     }
@@ -329,6 +330,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       const int h = h_first + hh;
       const uint32_t t1_addr = tmem_base + lane_base + BUF_BASE + buf * 128;
       if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 0);
+      // Dropout decisions for this thread's 32 (row, column) pairs of the step, generated before the
+      // T products are awaited so the integer work overlaps the tensor core.
+      uint32_t keep_bits = 0xffffffffu;
+      if constexpr (DROPOUT) {
+        const uint64_t head_base = args.drop.offset +
+                                   (static_cast<uint64_t>(b) * args.Hq + h) * args.M * static_cast<uint64_t>(args.N);
+        if constexpr (MODE == MODE_Q)
+          keep_bits = dropout_keep_word(args.drop, head_base + static_cast<uint64_t>(row) * args.N + col0);
+        else
+          keep_bits = dropout_keep_word_strided(args.drop, head_base + static_cast<uint64_t>(col0) * args.N + row,
+                                                static_cast<uint64_t>(args.N));
+      }
       {
         const bool w = wait(&t_full[buf], (i >> 1) & 1);
         if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }

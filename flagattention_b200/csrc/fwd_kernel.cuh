@@ -161,6 +161,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       if (mbar_try_wait(bar, parity)) return true;
       if ((++spins & 0xffu) == 0u) {
         if (*abort_flag) return false;
+        if (args.status != nullptr && *reinterpret_cast<volatile int32_t*>(args.status) != 0) return false;
         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
       }
     }
