@@ -85,6 +85,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
   constexpr uint64_t MN_DESC_B = make_smem_desc_hi(CHUNK_BYTES_B, 8 * Cfg::ROW_BYTES, Cfg::UMMA_SWZ);
   constexpr int N_ACC = MODE == MODE_KV ? 2 : (MODE == MODE_Q ? 1 : 0);
   constexpr uint32_t BUF_BASE = N_ACC * D;                  // TMEM column of buffer 0
+  // When TMEM has room, the resident tiles are copied into it once (tcgen05.cp) and the T products
+  // read their A operand from there: with 64-column steps those products are otherwise limited by
+  // shared-memory bandwidth (both operands streamed from shared memory for every step).
+  constexpr uint32_t A_BASE = BUF_BASE + 256;               // TMEM column of the resident copies
+  constexpr bool A_IN_TMEM = A_BASE + Sm::N_A * (D / 2) <= 512;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -228,6 +233,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       const uint32_t a_addr = smem_u32(sA);
       const uint32_t b_addr = smem_u32(sB);
       // T1 = A1 B1^T, T2 = A2 B2^T into buffer `buf` from ring stage `st`.
+      auto a_offset = [](int which, int s) -> uint32_t {
+        return which * Cfg::TILE_BYTES + (s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
+               (s % Cfg::STEPS_PER_CHUNK) * 32;
+      };
+      // Resident tiles -> TMEM, one K=16 slice (8 columns) per copy.
+      auto stage_resident = [&]() {
+        const uint64_t da = smem_desc(Cfg::KMAJOR_DESC, a_addr);
+#pragma unroll
+        for (int which = 0; which < Sm::N_A; ++which) {
+#pragma unroll
+          for (int s = 0; s < D / 16; ++s)
+            tmem_cp_128x256b_w(tmem_base + A_BASE + which * (D / 2) + s * 8, da + (a_offset(which, s) >> 4));
+        }
+      };
       auto issue_t = [&](int buf, int st) {
         const uint32_t t1 = tmem_base + BUF_BASE + buf * 128;
         const uint64_t da = smem_desc(Cfg::KMAJOR_DESC, a_addr);
@@ -236,14 +255,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         for (int which = 0; which < Sm::N_A; ++which) {
 #pragma unroll
           for (int s = 0; s < D / 16; ++s) {
-            constexpr int dummy = 0; (void)dummy;
-            const uint32_t a_off = which * Cfg::TILE_BYTES + (s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
-                                   (s % Cfg::STEPS_PER_CHUNK) * 32;
             const uint32_t b_off = which * Sm::B_TILE_BYTES + (s / Cfg::STEPS_PER_CHUNK) * CHUNK_BYTES_B +
                                    (s % Cfg::STEPS_PER_CHUNK) * 32;
             // offsets are multiples of 16 bytes and stay inside shared memory, so they add into
             // the 14-bit address field without carrying out of it
-            mma_ss_w(t1 + which * 64, da + (a_off >> 4), db + (b_off >> 4), IDESC_T, s > 0 ? 1u : 0u);
+            if constexpr (A_IN_TMEM) {
+              mma_ts_w(t1 + which * 64, tmem_base + A_BASE + which * (D / 2) + s * 8, db + (b_off >> 4),
+                       IDESC_T, s > 0 ? 1u : 0u);
+            } else {
+              mma_ss_w(t1 + which * 64, da + (a_offset(which, s) >> 4), db + (b_off >> 4), IDESC_T,
+                       s > 0 ? 1u : 0u);
+            }
           }
         }
       };
@@ -265,6 +287,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
+        if constexpr (A_IN_TMEM) stage_resident();
         issue_t(0, 0);
         tc_commit_w(&t_full[0]);
       }
@@ -329,7 +352,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       const int col0 = col_lo + (i - hh * steps_per_head) * STEP + wg * HALF;  // first column of this group
       const int h = h_first + hh;
       const uint32_t t1_addr = tmem_base + lane_base + BUF_BASE + buf * 128;
-      if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 0);
+      if (warp == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 0);
       // Dropout decisions for this thread's 32 (row, column) pairs of the step, generated before the
       // T products are awaited so the integer work overlaps the tensor core.
       uint32_t keep_bits = 0xffffffffu;
@@ -347,13 +370,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
       }
       tc_fence_after();
-      if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 1);
+      if (warp == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 1);
       uint32_t t1[HALF];
       uint32_t t2[MODE == MODE_TOTAL ? 1 : HALF];
       tmem_ld32(t1_addr + wg * HALF, t1);
       if constexpr (MODE != MODE_TOTAL) tmem_ld32(t1_addr + 64 + wg * HALF, t2);
       tmem_wait_ld();
-      if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 2);
+      if (warp == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 2);
 
       // Does this step cross the causal boundary for some row of the block?
       bool diag = false;
@@ -421,7 +444,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       }
       tc_fence_before();
       mbar_arrive(&p_ready[buf]);
-      if (warp == 0 && lane == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 3);
+      if (warp == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 3);
     }
 
     // ------------------------------------------------------------- epilogue

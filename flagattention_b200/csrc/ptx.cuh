@@ -221,6 +221,20 @@ __device__ __forceinline__ void tc_commit_w(uint64_t* bar) {
       : "memory");
 }
 
+// Copies a 128-row x 32-byte shared-memory matrix (given by a matrix descriptor, i.e. exactly one
+// K=16 slice of a 16-bit A operand) into 8 TMEM columns of all 128 lanes. Warp-uniform variant.
+__device__ __forceinline__ void tmem_cp_128x256b_w(uint32_t taddr, uint64_t desc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      ".reg .b32 rx;\n\t"
+      "elect.sync rx|q, 0xffffffff;\n\t"
+      "@q tcgen05.cp.cta_group::1.128x256b [%0], %1;\n\t"
+      "}\n" ::"r"(taddr),
+      "l"(desc)
+      : "memory");
+}
+
 // 32 lanes x 32-bit, N consecutive columns: thread i of the warp reads lane (base_lane + i).
 #define B200ATTN_R8(r, o) "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), \
                           "=r"(r[o + 4]), "=r"(r[o + 5]), "=r"(r[o + 6]), "=r"(r[o + 7])

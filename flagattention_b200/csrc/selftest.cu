@@ -66,7 +66,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   __syncwarp();
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
   const uint32_t tmem_a = tmem_base + 256;
-  if (args.a_in_tmem) {
+  if (args.a_in_tmem == 1) {
     // Row `tid` of A, packed two 16-bit values per 32-bit TMEM column.
     const uint32_t* row = reinterpret_cast<const uint32_t*>(args.a_gmem + tid * args.a_cols);
     for (int c = 0; c < args.a_cols / 2; c += 8) {
@@ -97,7 +97,12 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                     (s % args.b_chunk_steps) * args.b_step_bytes
                               : s * args.b_step_bytes;
         const uint64_t db = smem_desc(args.b_desc_hi, smem_u32(sB) + b_off);
-        if (args.a_in_tmem) {
+        if (args.a_in_tmem == 2) {
+          // A slice goes shared memory -> TMEM with tcgen05.cp, then feeds the MMA from TMEM.
+          const uint64_t da = smem_desc(args.a_desc_hi, smem_u32(sA) + a_off);
+          asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(tmem_a + s * 8), "l"(da) : "memory");
+          mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, s > 0 ? 1u : 0u);
+        } else if (args.a_in_tmem) {
           mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, s > 0 ? 1u : 0u);
         } else {
           const uint64_t da = smem_desc(args.a_desc_hi, smem_u32(sA) + a_off);

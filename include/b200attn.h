@@ -189,7 +189,7 @@ typedef struct {
   int32_t box_cols;    /* TMA box width in elements (<= 64)       */
   int32_t swizzle;     /* 0 none, 1 32B, 2 64B, 3 128B (TMA enum) */
   int32_t bf16;
-  int32_t a_in_tmem;   /* stage A through TMEM (packed 16-bit)    */
+  int32_t a_in_tmem;   /* 0: A from smem; 1: A stored to TMEM by threads; 2: smem -> TMEM by tcgen05.cp */
   int32_t n;           /* MMA N                                   */
   int32_t k_steps;     /* number of K=16 MMAs                     */
   uint32_t idesc;

@@ -84,3 +84,21 @@ def test_mnmajor_a(dtype):
     run(am, b, am.float().T @ b.float().T, box_cols=64, swizzle=3, a_in_tmem=0, n=128, k_steps=8,
         idesc=idesc(bf, 128, 128, 1, 0), a_desc_hi=desc_hi(16384, 1024, 2), b_desc_hi=desc_hi(16, 1024, 2),
         a_step_bytes=2048, b_step_bytes=32, b_chunk_steps=4, b_chunk_bytes=16384)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cols,row_bytes", [(128, 128), (64, 128), (32, 64), (16, 32)])
+def test_tmem_a_filled_by_tcgen05_cp(dtype, cols, row_bytes):
+    """A operand staged by TMA in shared memory, moved to TMEM one K=16 slice at a time with
+    tcgen05.cp (same descriptors as the shared-memory A operand), consumed from TMEM."""
+    dev = torch.device("cuda", 0)
+    bf = dtype == torch.bfloat16
+    a = torch.randn(128, cols, device=dev, dtype=dtype)
+    b = torch.randn(128, cols, device=dev, dtype=dtype)
+    us, ts = SW[row_bytes]
+    box = min(cols, 64)
+    run(a, b, a.float() @ b.float().T, box_cols=box, swizzle=ts, a_in_tmem=2, n=128, k_steps=cols // 16,
+        idesc=idesc(bf, 128, 128, 0, 0), a_desc_hi=desc_hi(16, 8 * row_bytes, us),
+        b_desc_hi=desc_hi(16, 8 * row_bytes, us), a_step_bytes=32, b_step_bytes=32,
+        a_chunk_steps=box // 16, b_chunk_steps=box // 16, a_chunk_bytes=128 * row_bytes,
+        b_chunk_bytes=128 * row_bytes)
