@@ -58,10 +58,10 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel on the default
 # workload, from the ncu capture summarised under profiles/ (None until captured).
 NCU_TRAFFIC_BYTES = {
-    # bwd_kernel<MODE_KV>: (170.5 + 22.9) MB measured at batch 2, scaled x2 to the batch-4 workload
-    # (traffic is proportional to batch); see profiles/fwd_kernel_bwd_kv_kernel_c2_batch2_full.md
-    "c2_gqa_prefill_train": {"bwd_kernel<kv>": 2 * (170.484224e6 + 22.904064e6),
-                             "fwd_kernel": 2 * (101.038336e6 + 32.596736e6)},
+    # (dram read + write) MB measured at batch 2, scaled x2 to the batch-4 workload (traffic is
+    # proportional to batch); the capture is summarised under profiles/
+    "c2_gqa_prefill_train": {"bwd_kernel<kv>": 2 * (220.867072e6 + 22.053632e6),
+                             "fwd_kernel": 2 * (101.170944e6 + 31.920384e6)},
 }
 
 
@@ -393,12 +393,15 @@ def main():
 
     # ---- device-resident timing --------------------------------------------------------------
     step = (lambda: ring_step()) if ring_step is not None else (lambda: run_step(cfg, q, k, v, do))
-    for _ in range(warmup):
-        step()
+    # The clock sampler starts before the warm-up (nvidia-smi takes a few hundred ms to come up) and
+    # runs through the timed region; warm-up steps are the same work, so every sample is under load.
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    barrier()
     if sampler:
         sampler.start()
+        time.sleep(0.3)
+    for _ in range(warmup):
+        step()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if ring_step is not None:
         ring.LAUNCHES = 0
