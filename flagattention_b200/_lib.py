@@ -79,6 +79,7 @@ class SelftestParams(Structure):
         ("a_chunk_steps", c_int32), ("b_chunk_steps", c_int32),
         ("a_chunk_bytes", c_int32), ("b_chunk_bytes", c_int32),
         ("status", c_void_p),
+        ("repeat", c_int32), ("cycles", c_void_p),
     ]
 
 

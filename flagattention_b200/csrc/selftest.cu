@@ -18,6 +18,8 @@ struct SelftestArgs {
   uint64_t a_desc_hi, b_desc_hi;
   int a_step_bytes, b_step_bytes, a_chunk_steps, b_chunk_steps, a_chunk_bytes, b_chunk_bytes;
   int32_t* status;
+  int repeat;            // issue the whole K loop this many times (timing runs)
+  long long* cycles;     // optional: clock64() ticks from first issue to completion
 };
 
 __global__ void __launch_bounds__(128, 1)
@@ -87,6 +89,8 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       failed = 1;
     } else {
       tc_fence_after();
+      const long long t_begin = clock64();
+      for (int rep = 0; rep < args.repeat; ++rep)
       for (int s = 0; s < args.k_steps; ++s) {
         const int a_off = args.a_chunk_steps > 0
                               ? (s / args.a_chunk_steps) * args.a_chunk_bytes +
@@ -101,12 +105,12 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           // A slice goes shared memory -> TMEM with tcgen05.cp, then feeds the MMA from TMEM.
           const uint64_t da = smem_desc(args.a_desc_hi, smem_u32(sA) + a_off);
           asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(tmem_a + s * 8), "l"(da) : "memory");
-          mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, s > 0 ? 1u : 0u);
+          mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, (s > 0 || rep > 0) ? 1u : 0u);
         } else if (args.a_in_tmem) {
-          mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, s > 0 ? 1u : 0u);
+          mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, (s > 0 || rep > 0) ? 1u : 0u);
         } else {
           const uint64_t da = smem_desc(args.a_desc_hi, smem_u32(sA) + a_off);
-          mma_ss(tmem_base, da, db, args.idesc, s > 0 ? 1u : 0u);
+          mma_ss(tmem_base, da, db, args.idesc, (s > 0 || rep > 0) ? 1u : 0u);
         }
       }
       tc_commit(&bar_mma);
@@ -114,6 +118,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         report_status(args.status, ST_WAIT_MMA);
         failed = 1;
       }
+      if (args.cycles != nullptr) *args.cycles = clock64() - t_begin;
     }
   }
   __syncthreads();
@@ -180,6 +185,8 @@ extern "C" int b200attn_umma_selftest(const b200attn_selftest_params* p, void* s
   a.a_chunk_steps = p->a_chunk_steps; a.b_chunk_steps = p->b_chunk_steps;
   a.a_chunk_bytes = p->a_chunk_bytes; a.b_chunk_bytes = p->b_chunk_bytes;
   a.status = p->status;
+  a.repeat = p->repeat > 0 ? p->repeat : 1;
+  a.cycles = p->cycles;
   const int smem_bytes = 65536 + 1024;
   static bool attr_set = false;
   if (!attr_set) {

@@ -198,6 +198,8 @@ typedef struct {
   int32_t a_chunk_steps, b_chunk_steps; /* K steps per TMA chunk (0 = all in one) */
   int32_t a_chunk_bytes, b_chunk_bytes; /* byte jump between chunks                */
   int32_t* status;
+  int32_t repeat;      /* issue the K loop this many times, accumulating (0 = once)        */
+  long long* cycles;   /* optional device int64: SM clock ticks from first issue to done   */
 } b200attn_selftest_params;
 
 int b200attn_umma_selftest(const b200attn_selftest_params* p, void* stream);
