@@ -1,5 +1,7 @@
 """B200-native drop-in for ``flag_attn.flash_attention``."""
-from .flash import FlashAttentionFunction, check_device_status, flash_attention  # noqa: F401
+from .flash import (FlashAttentionFunction, check_device_status, flash_attention,  # noqa: F401
+                    flash_attention_split_kv)
 
-__all__ = ["flash_attention", "FlashAttentionFunction", "check_device_status"]
+__all__ = ["flash_attention", "flash_attention_split_kv", "FlashAttentionFunction",
+           "check_device_status"]
 __version__ = "0.1.0"

@@ -97,6 +97,7 @@ SYMBOLS = {
     "b200attn_dropout_mask": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_float, c_uint64,
                                         c_uint64, c_void_p]),
     "b200attn_fwd_splitkv": (c_int32, [POINTER(SplitKVParams), c_void_p]),
+    "b200attn_splitkv_num_splits": (c_int32, [c_int32] * 7),
     "b200attn_merge_partial": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200attn_abi_version": (c_int32, []),

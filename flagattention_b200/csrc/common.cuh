@@ -27,7 +27,7 @@ int cuda_fail(cudaError_t e, const char* what);
 // `swizzle` is a CUtensorMapSwizzle value. Returns 0 or a negative B200ATTN_E* code.
 int encode_tmap_4d(CUtensorMap* out, const b200attn_tensor& t, int elem_bytes, int64_t B, int64_t H,
                    int64_t rows, int64_t D, int box_cols, int box_rows, int swizzle,
-                   const char* name);
+                   const char* name, int box_heads = 1);
 
 // Checks the TMA requirements of one operand; returns 0 or B200ATTN_EINVAL.
 int check_tma_operand(const b200attn_tensor& t, int elem_bytes, const char* name);

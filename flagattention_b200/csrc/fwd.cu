@@ -1,4 +1,5 @@
 // C entry point of the forward pass: argument validation, TMA descriptors, dispatch on D.
+#include "decode.cuh"
 #include "fwd_launch.cuh"
 
 namespace b200attn {
@@ -84,6 +85,9 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
   a.lse_stride_split = 0;
   a.num_splits = 1;
   a.tiles_per_split = cdiv(p->N, 128);
+  a.pack_heads = 0;
+  a.dual_stream = 0;
+  a.ring_stages = 0;
   a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
   a.groups = p->Hq / p->Hkv;
   a.causal = p->causal ? 1 : 0;
@@ -145,6 +149,21 @@ __global__ void splitkv_combine_kernel(const float* __restrict__ part_o, const f
   if (threadIdx.x == 0) lse[row] = denom > 0.f ? mx + logf(denom) : -INFINITY;
 }
 
+static int launch_splitkv_combine(const b200attn_splitkv_params* p, bool bf16, unsigned rows,
+                                  cudaStream_t stream) {
+  if (bf16) {
+    splitkv_combine_kernel<true><<<rows, 128, 0, stream>>>(
+        p->part_o, p->part_lse, p->o.ptr, p->lse, p->o.stride[0], p->o.stride[1], p->o.stride[2], p->Hq,
+        p->M, p->D, p->num_splits);
+  } else {
+    splitkv_combine_kernel<false><<<rows, 128, 0, stream>>>(
+        p->part_o, p->part_lse, p->o.ptr, p->lse, p->o.stride[0], p->o.stride[1], p->o.stride[2], p->Hq,
+        p->M, p->D, p->num_splits);
+  }
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
+}
+
 }  // namespace b200attn
 
 extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stream_) {
@@ -176,6 +195,58 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
     set_error("fwd_splitkv: grid too large");
     return B200ATTN_EINVAL;
   }
+  const int64_t rows = static_cast<int64_t>(p->B) * p->Hq * p->M;
+  if (rows > 2147483647ll) {
+    set_error("fwd_splitkv: too many rows for the combine grid");
+    return B200ATTN_EINVAL;
+  }
+  const bool bf16 = p->dtype == B200ATTN_BF16;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if ((p->Hq / p->Hkv) * static_cast<int64_t>(p->M) <= DECODE_MAX_ROWS) {
+    // A few query rows per KV head: register-resident streaming kernel, no tensor-core tile.
+    int rc = check_tma_operand(p->q, 2, "q");
+    if (rc == B200ATTN_OK) rc = check_tma_operand(p->k, 2, "k");
+    if (rc == B200ATTN_OK) rc = check_tma_operand(p->v, 2, "v");
+    if (rc != B200ATTN_OK) return rc;
+    const b200attn_tensor* ops[3] = {&p->q, &p->k, &p->v};
+    const int64_t ext[3][3] = {{p->B, p->Hq, p->M}, {p->B, p->Hkv, p->N}, {p->B, p->Hkv, p->N}};
+    for (int t = 0; t < 3; ++t) {
+      for (int i = 0; i < 3; ++i) {
+        if (ext[t][i] > 1 && ops[t]->stride[i] % 8 != 0) {
+          set_error("fwd_splitkv: batch / head / row strides of q, k, v must be multiples of 8 elements");
+          return B200ATTN_EINVAL;
+        }
+      }
+    }
+    if (p->o.stride[3] != 1) {
+      set_error("fwd_splitkv: o needs feature stride 1");
+      return B200ATTN_EINVAL;
+    }
+    DecodeArgs d{};
+    d.q = static_cast<const uint16_t*>(p->q.ptr);
+    d.k = static_cast<const uint16_t*>(p->k.ptr);
+    d.v = static_cast<const uint16_t*>(p->v.ptr);
+    d.q_sb = p->q.stride[0]; d.q_sh = p->q.stride[1]; d.q_sm = p->q.stride[2];
+    d.k_sb = p->k.stride[0]; d.k_sh = p->k.stride[1]; d.k_sn = p->k.stride[2];
+    d.v_sb = p->v.stride[0]; d.v_sh = p->v.stride[1]; d.v_sn = p->v.stride[2];
+    d.part_o = p->part_o;
+    d.part_lse = p->part_lse;
+    d.B = p->B; d.Hq = p->Hq; d.Hkv = p->Hkv; d.M = p->M; d.N = p->N;
+    d.groups = p->Hq / p->Hkv;
+    d.num_splits = p->num_splits;
+    d.keys_per_split = cdiv(n_blocks, S) * 128;
+    d.causal = p->causal ? 1 : 0;
+    d.qk_scale = p->sm_scale * 1.4426950408889634f;
+    if (p->num_splits == 1) {
+      d.final_o = static_cast<uint16_t*>(p->o.ptr);
+      d.final_lse = p->lse;
+      d.o_sb = p->o.stride[0]; d.o_sh = p->o.stride[1]; d.o_sm = p->o.stride[2];
+      return launch_decode_partial(d, p->D, bf16, stream);
+    }
+    rc = launch_decode_partial(d, p->D, bf16, stream);
+    if (rc) return rc;
+    return launch_splitkv_combine(p, bf16, static_cast<unsigned>(rows), stream);
+  }
   // Partial pass: the forward kernel restricted to a K/V tile range per CTA, writing fp32
   // partial O (normalised within the split) and the split's log-normaliser.
   b200attn_fwd_params f{};
@@ -190,6 +261,16 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
     default: rc = make_fwd_tmaps<128>(&f, L); break;
   }
   if (rc) return rc;
+  // Decode-style shapes with grouped heads: all query heads of a KV head share one 128-row tile, so
+  // every K/V tile is fetched once per KV head instead of once per query head.
+  const int groups = p->Hq / p->Hkv;
+  const bool packed = groups > 1 && groups * p->M <= 128;
+  if (packed) {
+    const int chunk = p->D >= 64 ? 64 : p->D;
+    const int swz = p->D >= 64 ? 3 : (p->D == 32 ? 2 : 1);
+    rc = encode_tmap_4d(&L.tmQ, p->q, 2, p->B, p->Hq, p->M, p->D, chunk, p->M, swz, "q", groups);
+    if (rc) return rc;
+  }
   const int64_t MD = static_cast<int64_t>(p->M) * p->D;
   FwdArgs& a = L.args;
   a.o = p->part_o;
@@ -201,8 +282,16 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
   a.lse_stride_b = static_cast<int64_t>(p->Hq) * p->num_splits * p->M;
   a.lse_stride_h = static_cast<int64_t>(p->num_splits) * p->M;
   a.lse_stride_split = p->M;
-  a.num_splits = p->num_splits;
-  a.tiles_per_split = cdiv(n_blocks, S);
+  // With an even split count the packed mode runs two partials per CTA (one per query tile).
+  const bool dual = packed && p->num_splits % 2 == 0;
+  const int cta_splits = dual ? p->num_splits / 2 : p->num_splits;
+  a.num_splits = cta_splits;
+  a.tiles_per_split = cdiv(n_blocks, cta_splits < n_blocks ? cta_splits : n_blocks);
+  a.pack_heads = packed ? groups : 0;
+  a.dual_stream = dual ? 1 : 0;
+  a.ring_stages = p->D == 128 ? FwdSmem<128>::DUAL_STAGES
+                  : p->D == 64 ? FwdSmem<64>::DUAL_STAGES
+                  : p->D == 32 ? FwdSmem<32>::DUAL_STAGES : FwdSmem<16>::DUAL_STAGES;
   a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
   a.groups = p->Hq / p->Hkv;
   a.causal = p->causal ? 1 : 0;
@@ -211,9 +300,9 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
   a.qk_scale = p->sm_scale * 1.4426950408889634f;
   a.drop = make_dropout_ctx(0.f, 0, 0);
   a.status = p->status;
-  a.n_zblocks = cdiv(p->M, 256) * p->num_splits;
-  a.grid_chunk = grid_chunk(a.groups, 4ll * p->N * p->D, a.causal != 0);
-  L.grid = dim3(static_cast<unsigned>(static_cast<int64_t>(p->B) * p->Hq * a.n_zblocks));
+  a.n_zblocks = cdiv(p->M, 256) * cta_splits;
+  a.grid_chunk = packed ? 1 : grid_chunk(a.groups, 4ll * p->N * p->D, a.causal != 0);
+  L.grid = dim3(static_cast<unsigned>(static_cast<int64_t>(p->B) * (packed ? p->Hkv : p->Hq) * a.n_zblocks));
   L.bf16 = p->dtype == B200ATTN_BF16;
   L.dropout = false;
   L.stream = static_cast<cudaStream_t>(stream_);
@@ -224,20 +313,78 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
     default: rc = launch_fwd_d128(L); break;
   }
   if (rc) return rc;
-  const int64_t rows = static_cast<int64_t>(p->B) * p->Hq * p->M;
-  if (rows > 2147483647ll) {
-    set_error("fwd_splitkv: too many rows for the combine grid");
-    return B200ATTN_EINVAL;
+  return launch_splitkv_combine(p, L.bf16, static_cast<unsigned>(rows), L.stream);
+}
+
+namespace b200attn {
+namespace {
+
+int cached_sm_count() {
+  static int counts[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < 64 && counts[dev] > 0) return counts[dev];
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  if (dev >= 0 && dev < 64) counts[dev] = n;
+  return n;
+}
+
+}  // namespace
+}  // namespace b200attn
+
+extern "C" int b200attn_splitkv_num_splits(int32_t B, int32_t Hq, int32_t Hkv, int32_t M, int32_t N,
+                                           int32_t D, int32_t num_sms) {
+  using namespace b200attn;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || M <= 0 || N <= 0 || Hq % Hkv != 0) return 1;
+  if (num_sms <= 0) num_sms = cached_sm_count();
+  const int groups = Hq / Hkv;
+  const int n_blocks = cdiv(N, 128);
+  if (static_cast<int64_t>(groups) * M <= DECODE_MAX_ROWS) {
+    // Streaming kernel: light CTAs, two or three resident per SM. Choose the smallest split count
+    // whose CTAs keep the resident slots at least 90 % as busy as the best count does, with at
+    // least 512 keys per split so that the merge stays a small fraction of the work.
+    const int64_t units = static_cast<int64_t>(B) * Hkv;
+    const int64_t slots = static_cast<int64_t>(num_sms) * decode_resident_ctas(groups * M);
+    int cap = cdiv(n_blocks, 4);
+    if (cap > 128) cap = 128;
+    auto busy = [&](int s) {
+      const int64_t ctas = units * s;
+      return static_cast<double>(ctas) / static_cast<double>(cdiv(ctas, slots) * slots);
+    };
+    auto admissible = [&](int s) {
+      const int per = cdiv(n_blocks, s);
+      return s == 1 || per * s - n_blocks < per;  // no empty split
+    };
+    double best = 0.0;
+    for (int s = 1; s <= cap; ++s)
+      if (admissible(s) && busy(s) > best) best = busy(s);
+    for (int s = 1; s <= cap; ++s)
+      if (admissible(s) && busy(s) >= 0.9 * best) return s;
+    return 1;
   }
-  if (L.bf16) {
-    splitkv_combine_kernel<true><<<static_cast<unsigned>(rows), 128, 0, L.stream>>>(
-        p->part_o, p->part_lse, p->o.ptr, p->lse, p->o.stride[0], p->o.stride[1], p->o.stride[2], p->Hq,
-        p->M, p->D, p->num_splits);
-  } else {
-    splitkv_combine_kernel<false><<<static_cast<unsigned>(rows), 128, 0, L.stream>>>(
-        p->part_o, p->part_lse, p->o.ptr, p->lse, p->o.stride[0], p->o.stride[1], p->o.stride[2], p->Hq,
-        p->M, p->D, p->num_splits);
-  }
-  B200ATTN_CUDA_OK(cudaGetLastError());
-  return B200ATTN_OK;
+  // Tensor-core kernel: one CTA per SM. The smallest CTA count per unit whose last wave is at least
+  // 85 % as full as the best achievable, with at least four 128-key tiles per CTA. In the packed
+  // mode every CTA carries two partials (one per query tile), so the split count is twice that.
+  const bool packed = groups > 1 && groups * M <= 128;
+  const int64_t ctas = static_cast<int64_t>(B) * (packed ? Hkv : Hq) * cdiv(M, 256);
+  const int per_cta = packed ? 2 : 1;
+  if (!packed && ctas >= 0.8 * num_sms) return 1;
+  int limit = n_blocks / 4;
+  if (limit > 128 / per_cta) limit = 128 / per_cta;
+  if (limit < 1) return n_blocks >= 2 ? per_cta : 1;
+  auto admissible = [&](int s) {
+    const int per = cdiv(n_blocks, s);
+    return s == 1 || per * s - n_blocks < per;
+  };
+  auto eff = [&](int s) {
+    const double waves = static_cast<double>(ctas) * s / num_sms;
+    return waves / ceil(waves);
+  };
+  double best = 0.0;
+  for (int s = 1; s <= limit; ++s)
+    if (admissible(s) && eff(s) > best) best = eff(s);
+  for (int s = 1; s <= limit; ++s)
+    if (admissible(s) && eff(s) >= 0.85 * best) return s * per_cta;
+  return 1;
 }

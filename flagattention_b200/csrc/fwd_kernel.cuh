@@ -47,6 +47,13 @@ struct FwdArgs {
   int64_t lse_stride_b, lse_stride_h, lse_stride_split;
   int n_zblocks, grid_chunk;        // grid order, see decode_block()
   int num_splits, tiles_per_split;  // split-KV: CTA `split` visits K/V tiles [split*tps, (split+1)*tps)
+  int pack_heads;                   // > 0: decode-style packing, the CTA's tile 0 holds all `groups`
+                                    // query heads of one KV head (rows = head-major, M rows each,
+                                    // groups * M <= 128) so K/V are streamed once per KV head
+  int dual_stream;                  // with pack_heads: tile 1 holds the same rows as tile 0 and the two
+                                    // tiles take alternate K/V tiles of the CTA's key range, as two
+                                    // independent softmax chains; tile t writes partial 2 * split + t
+  int ring_stages;                  // dual_stream: K/V ring depth (one shared Q tile leaves room for more)
   int B, Hq, Hkv, M, N, groups;
   int causal, o_fp32;
   float sm_scale, qk_scale;
@@ -61,6 +68,12 @@ struct FwdSmem {
   static constexpr int KV_BYTES = STAGES * TileCfg<D>::TILE_BYTES;
   static constexpr int BAR_OFFSET = Q_BYTES + 2 * KV_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;  // barriers + alignment slack
+  // Dual-stream mode: one Q tile, as deep a ring as fits (at most 8 stages: the barrier block
+  // holds 10 + 4 * stages barriers in 512 bytes).
+  static constexpr int MAX_TOTAL = 232448;
+  static constexpr int DUAL_STAGES_FIT = (MAX_TOTAL - 1536 - TileCfg<D>::TILE_BYTES) / (2 * TileCfg<D>::TILE_BYTES);
+  static constexpr int DUAL_STAGES = DUAL_STAGES_FIT > 8 ? 8 : DUAL_STAGES_FIT;
+  static constexpr int DUAL_TOTAL = (1 + 2 * DUAL_STAGES) * TileCfg<D>::TILE_BYTES + 512 + 1024;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -83,16 +96,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  // Layout: Q tiles | K ring | V ring | barriers. The dual-stream mode keeps one Q tile (both query
+  // tiles hold the same rows) and spends the space on a deeper ring.
+  const bool dual = args.pack_heads > 0 && args.dual_stream != 0;
+  const int stages = dual ? args.ring_stages : STAGES;
   uint8_t* sQ = smem;
-  uint8_t* sK = smem + Sm::Q_BYTES;
-  uint8_t* sV = sK + Sm::KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Sm::BAR_OFFSET);
+  uint8_t* sK = smem + (dual ? 1 : 2) * Cfg::TILE_BYTES;
+  uint8_t* sV = sK + stages * Cfg::TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + stages * Cfg::TILE_BYTES);
   uint64_t* q_full = bars;                  // [2]
-  uint64_t* k_full = bars + 2;              // [STAGES]
-  uint64_t* k_empty = k_full + STAGES;      // [STAGES]
-  uint64_t* v_full = k_empty + STAGES;      // [STAGES]
-  uint64_t* v_empty = v_full + STAGES;      // [STAGES]
-  uint64_t* s_full = v_empty + STAGES;      // [2]
+  uint64_t* k_full = bars + 2;              // [stages]
+  uint64_t* k_empty = k_full + stages;      // [stages]
+  uint64_t* v_full = k_empty + stages;      // [stages]
+  uint64_t* v_empty = v_full + stages;      // [stages]
+  uint64_t* s_full = v_empty + stages;      // [2]
   uint64_t* p_half = s_full + 2;            // [2 tiles][2 halves]
   uint64_t* o_full = p_half + 4;            // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
@@ -100,13 +117,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const BlockCoord bc = decode_block(blockIdx.x, args.B * args.Hq, args.n_zblocks, args.grid_chunk);
+  const bool packed = args.pack_heads > 0;
+  const int grid_heads = packed ? args.Hkv : args.Hq;
+  const BlockCoord bc = decode_block(blockIdx.x, args.B * grid_heads, args.n_zblocks, args.grid_chunk);
   const int split = bc.z % args.num_splits;
   const int m_blk = args.n_zblocks / args.num_splits - 1 - bc.z / args.num_splits;  // longest first
   const int j0 = split * args.tiles_per_split;  // first K/V tile of this CTA
-  const int h = bc.bh % args.Hq;
-  const int b = bc.bh / args.Hq;
-  const int hk = h / args.groups;
+  const int b = bc.bh / grid_heads;
+  const int hk = packed ? bc.bh % grid_heads : (bc.bh % grid_heads) / args.groups;
+  const int h = packed ? hk * args.groups : bc.bh % grid_heads;   // first (or only) query head
   const int m0 = m_blk * 2 * BLOCK;
   const int P_SEQ = args.N - args.M;
 
@@ -117,15 +136,26 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const int mt = m0 + t * BLOCK;
     int hi = args.N;
     if (args.causal) hi = min(args.N, max(0, P_SEQ + mt + BLOCK));
-    const int n_full = mt < args.M ? cdiv(hi, BLOCK) : 0;
+    int n_full = mt < args.M ? cdiv(hi, BLOCK) : 0;
+    if (packed) {
+      // one tile holds every row of every head of the group: rows m = 0..M-1
+      const int hi_p = args.causal ? min(args.N, max(0, P_SEQ + args.M)) : args.N;
+      n_full = t == 0 ? cdiv(hi_p, BLOCK) : 0;
+    }
     n_tiles[t] = max(0, min(n_full, j0 + args.tiles_per_split) - j0);
   }
-  const int n_max = max(n_tiles[0], n_tiles[1]);
+  if (dual) {
+    const int n = n_tiles[0];
+    n_tiles[0] = (n + 1) / 2;
+    n_tiles[1] = n / 2;
+  }
+  // Number of K/V tiles the CTA streams.
+  const int n_max = dual ? n_tiles[0] + n_tiles[1] : max(n_tiles[0], n_tiles[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full[0], 1);
     mbar_init(&q_full[1], 1);
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
@@ -176,16 +206,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
-      for (int t = 0; t < 2; ++t) {
+      for (int t = 0; t < (dual ? 1 : 2); ++t) {
         if (n_tiles[t] == 0) continue;
-        mbar_expect_tx(&q_full[t], Cfg::TILE_BYTES);
+        // packed: the box is [groups heads x M rows x CHUNK], landing head-major in the tile
+        mbar_expect_tx(&q_full[t], packed ? args.groups * args.M * D * 2 : Cfg::TILE_BYTES);
         for (int c = 0; c < Cfg::NCHUNK; ++c)
           tma_load_4d(sQ + t * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &q_full[t],
-                      c * Cfg::CHUNK, m0 + t * BLOCK, h, b);
+                      c * Cfg::CHUNK, packed ? 0 : m0 + t * BLOCK, h, b);
       }
-      for (int j = 0; j < n_max; ++j) {
-        const int st = j % STAGES;
-        const uint32_t par = ((j / STAGES) & 1) ^ 1;  // first pass over the ring passes at once
+      int st = 0;
+      uint32_t par = 1;  // first pass over the ring passes at once
+      for (int j = 0; j < n_max; ++j, ++st) {
+        if (st == stages) { st = 0; par ^= 1; }
         if (!wait(&k_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
         mbar_expect_tx(&k_full[st], Cfg::TILE_BYTES);
         for (int c = 0; c < Cfg::NCHUNK; ++c)
@@ -211,7 +243,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const uint32_t k_addr = smem_u32(sK);
       const uint32_t v_addr = smem_u32(sV);
       auto issue_qk = [&](int t, int st) {
-        const uint64_t dq = smem_desc(Cfg::KMAJOR_DESC, q_addr + t * Cfg::TILE_BYTES);
+        const uint64_t dq = smem_desc(Cfg::KMAJOR_DESC, q_addr + (dual ? 0 : t) * Cfg::TILE_BYTES);
         const uint64_t dk = smem_desc(Cfg::KMAJOR_DESC, k_addr + st * Cfg::TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < D / 16; ++s) {
@@ -237,8 +269,47 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         return false;
       };
       bool ok = true;
+      if (dual) {
+        // Two independent chains: K/V tile j belongs to query tile j & 1.
+        if (!wait_all(&q_full[0], 0, ST_WAIT_TMA)) ok = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (n_tiles[t] == 0) continue;
+          if (!wait_all(&k_full[t], 0, ST_WAIT_TMA)) { ok = false; break; }  // stages >= 2
+          tc_fence_after();
+          issue_qk(t, t);
+          tc_commit_w(&s_full[t]);
+          tc_commit_w(&k_empty[t]);
+        }
+        int st = 0, st2 = 2 % stages;               // ring slots of tiles j and j + 2
+        uint32_t ph = 0, ph2 = stages == 2 ? 1 : 0;  // and the phases of their "full" barriers
+        for (int j = 0; j < n_max && ok; ++j) {
+          const int t = j & 1, jj = j >> 1;
+          const bool more = j + 2 < n_max;
+          if (!wait_all(&v_full[st], ph, ST_WAIT_TMA)) break;
+          if (more) {
+            if (!wait_all(&k_full[st2], ph2, ST_WAIT_TMA)) break;
+          }
+          if (!wait_all(&p_half[2 * t], jj & 1, ST_WAIT_SOFTMAX)) break;
+          tc_fence_after();
+          issue_pv(t, st, jj > 0, 0);
+          if (!wait_all(&p_half[2 * t + 1], jj & 1, ST_WAIT_SOFTMAX)) break;
+          tc_fence_after();
+          issue_pv(t, st, jj > 0, 1);
+          if (more) {
+            issue_qk(t, st2);
+            tc_commit_w(&s_full[t]);
+          } else {
+            tc_commit_w(&o_full[t]);
+          }
+          tc_commit_w(&v_empty[st]);
+          if (more) tc_commit_w(&k_empty[st2]);
+          if (++st == stages) { st = 0; ph ^= 1; }
+          if (++st2 == stages) { st2 = 0; ph2 ^= 1; }
+        }
+        ok = false;  // skip the shared-tile loop below
+      }
       // Prologue: S_t = Q_t K_0^T for both tiles.
-      ok = wait_all(&k_full[0], 0, ST_WAIT_TMA);
+      if (ok) ok = wait_all(&k_full[0], 0, ST_WAIT_TMA);
       for (int t = 0; t < 2 && ok; ++t) {
         if (n_tiles[t] == 0) continue;
         if (!wait_all(&q_full[t], 0, ST_WAIT_TMA)) { ok = false; break; }
@@ -280,7 +351,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     reg_alloc<208>();
     const int t = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
-    const int m_glob = m0 + t * BLOCK + row;
+    // Query row and head of this thread; in packed mode rows are (head, m) pairs, head-major.
+    const int h_row = packed ? h + row / args.M : h;
+    // (rows without a query, and tile 1 when it is unused, get the out-of-range position M)
+    const int m_glob = packed ? ((row < args.groups * args.M && (dual || t == 0)) ? row % args.M : args.M)
+                              : m0 + t * BLOCK + row;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tmem_s = tmem_base + lane_base + t * BLOCK;
     const uint32_t tmem_o = tmem_base + lane_base + 2 * BLOCK + t * D;
@@ -289,30 +364,40 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     // Keys n < lim are visible to this row.
     const int lim = args.causal ? min(args.N, P_SEQ + m_glob + 1) : args.N;
     // Tiles j with (j+1)*128 <= full_upto need no masking for any row of the tile.
-    const int full_upto = args.causal ? min(args.N, P_SEQ + m0 + t * BLOCK + 1) : args.N;
+    const int full_upto = args.causal ? min(args.N, P_SEQ + (packed ? 0 : m0 + t * BLOCK) + 1) : args.N;
+    const int split_out = dual ? 2 * split + t : split;
     uint64_t ctr_row = 0;
     if constexpr (DROPOUT) {
       ctr_row = args.drop.offset +
-                ((static_cast<uint64_t>(b) * args.Hq + h) * args.M + static_cast<uint64_t>(m_glob)) *
+                ((static_cast<uint64_t>(b) * args.Hq + h_row) * args.M + static_cast<uint64_t>(m_glob)) *
                     static_cast<uint64_t>(args.N);
     }
 
     float m_run = -INFINITY;
     float l_run = 0.f;
     bool ok = true;
+    const bool warp_idle = packed && (warp & 3) * 32 >= args.groups * args.M;
 
     for (int j = 0; j < nt; ++j) {
       // Dropout decisions of this row for the tile's 128 keys, generated before S is awaited so the
       // integer work overlaps the tensor core instead of extending the softmax phase.
+      const int jg = j0 + (dual ? 2 * j + t : j);  // K/V tile index within the sequence
       uint32_t keep_bits[DROPOUT ? 4 : 1];
       if constexpr (DROPOUT) {
-        const uint64_t base = ctr_row + static_cast<uint64_t>((j0 + j) * BLOCK);
+        const uint64_t base = ctr_row + static_cast<uint64_t>(jg * BLOCK);
 #pragma unroll
         for (int w = 0; w < 4; ++w) keep_bits[w] = dropout_keep_word(args.drop, base + 32 * w);
       }
       {
         const bool w = wait(&s_full[t], j & 1);
         if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
+      }
+      if (warp_idle) {
+        // No query row lives in this warp's 32 tile rows: keep the barrier protocol, skip the math
+        // (whatever the P V product makes of these rows is never stored).
+        mbar_arrive(&p_half[2 * t + 0]);
+        mbar_arrive(&p_half[2 * t + 1]);
+        continue;
       }
       tc_fence_after();
       uint32_t s[128];
@@ -322,8 +407,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       tmem_ld32(tmem_s + 96, s + 96);
       tmem_wait_ld();
 
-      if ((j0 + j + 1) * BLOCK > full_upto) {
-        const int base = (j0 + j) * BLOCK;
+      if ((jg + 1) * BLOCK > full_upto) {
+        const int base = jg * BLOCK;
 #pragma unroll
         for (int i = 0; i < 128; ++i)
           if (base + i >= lim) s[i] = 0xff800000u;  // -inf
@@ -403,7 +488,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     if (ok && m_glob < args.M) {
       const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
       const float lse = empty ? -INFINITY : m_run * args.sm_scale + logf(l_run);
-      args.lse[b * args.lse_stride_b + h * args.lse_stride_h + split * args.lse_stride_split + m_glob] = lse;
+      args.lse[b * args.lse_stride_b + h_row * args.lse_stride_h + split_out * args.lse_stride_split + m_glob] = lse;
     }
     if (ok) {
       tc_fence_after();
@@ -411,7 +496,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
       float inv = empty ? 0.f : 1.0f / l_run;
       if constexpr (DROPOUT) inv *= args.drop.inv_keep;
-      const int64_t o_off = b * args.o_stride_b + h * args.o_stride_h + split * args.o_stride_split +
+      const int64_t o_off = b * args.o_stride_b + h_row * args.o_stride_h + split_out * args.o_stride_split +
                             static_cast<int64_t>(m_glob) * args.o_stride_m;
 #pragma unroll
       for (int c = 0; c < D; c += 16) {

@@ -16,12 +16,13 @@ struct FwdLaunch {
 template <int D, bool BF16, bool DROPOUT>
 int launch_fwd_variant(const FwdLaunch& L) {
   auto kernel = fwd_kernel<D, BF16, DROPOUT>;
-  constexpr int smem = FwdSmem<D>::TOTAL;
+  constexpr int smem_max = FwdSmem<D>::TOTAL > FwdSmem<D>::DUAL_TOTAL ? FwdSmem<D>::TOTAL : FwdSmem<D>::DUAL_TOTAL;
+  const int smem = L.args.dual_stream ? FwdSmem<D>::DUAL_TOTAL : FwdSmem<D>::TOTAL;
   static bool attr_done[64] = {};
   int dev = 0;
   B200ATTN_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-    B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
   kernel<<<L.grid, 384, smem, L.stream>>>(L.tmQ, L.tmK, L.tmV, L.args);

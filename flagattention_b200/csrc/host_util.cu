@@ -60,7 +60,7 @@ int check_tma_operand(const b200attn_tensor& t, int elem_bytes, const char* name
 
 int encode_tmap_4d(CUtensorMap* out, const b200attn_tensor& t, int elem_bytes, int64_t B, int64_t H,
                    int64_t rows, int64_t D, int box_cols, int box_rows, int swizzle,
-                   const char* name) {
+                   const char* name, int box_heads) {
   int rc = check_tma_operand(t, elem_bytes, name);
   if (rc != B200ATTN_OK) return rc;
   EncodeTiledFn fn = get_encode_fn();
@@ -89,8 +89,8 @@ int encode_tmap_4d(CUtensorMap* out, const b200attn_tensor& t, int elem_bytes, i
     fallback = sb * (ext[i] > 0 ? ext[i] : 1);
     if (fallback % 16 != 0 || fallback >= (1ll << 40)) fallback = D * elem_bytes;
   }
-  const cuuint32_t box[4] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1u,
-                             1u};
+  const cuuint32_t box[4] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows),
+                             static_cast<cuuint32_t>(box_heads), 1u};
   const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
   const CUtensorMapDataType dt =
       elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;

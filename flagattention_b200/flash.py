@@ -61,6 +61,76 @@ def _vec_ready(x: torch.Tensor) -> torch.Tensor:
     return _tma_ready(x)
 
 
+_SM_COUNT = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    n = _SM_COUNT.get(idx)
+    if n is None:
+        n = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
+
+
+def _split_kv_forward(lib, q, k, v, causal, sm_scale, num_sms, stream, status):
+    """Split-KV forward on TMA-ready q, k, v: returns (o in q.dtype, log-normaliser [B, H, M])."""
+    B, H, M, D = q.shape
+    Hk, N = k.shape[1], k.shape[2]
+    device = q.device
+    S = int(lib.b200attn_splitkv_num_splits(B, H, Hk, M, N, D, num_sms))
+    o = torch.empty((B, H, M, D), dtype=q.dtype, device=device)
+    L = torch.empty((B, H, M), device=device, dtype=torch.float32)
+    if S > 1:
+        part_o = torch.empty((B, H, S, M, D), dtype=torch.float32, device=device)
+        part_l = torch.empty((B, H, S, M), dtype=torch.float32, device=device)
+        part_o_ptr, part_l_ptr = part_o.data_ptr(), part_l.data_ptr()
+    elif (H // Hk) * M <= 2:
+        part_o_ptr = part_l_ptr = L.data_ptr()  # unused by the single-split streaming kernel
+    else:
+        fp = _lib.FwdParams(
+            _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), L.data_ptr(),
+            B, H, Hk, M, N, D, _lib.dtype_code(q.dtype), _lib.dtype_code(q.dtype),
+            int(causal), sm_scale, 0.0, 0, 0, status.data_ptr())
+        _lib.check(lib.b200attn_fwd(fp, stream), "b200attn_fwd")
+        return o, L
+    sp = _lib.SplitKVParams(
+        _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o),
+        L.data_ptr(), part_o_ptr, part_l_ptr,
+        B, H, Hk, M, N, D, S, _lib.dtype_code(q.dtype), int(causal), sm_scale, status.data_ptr())
+    _lib.check(lib.b200attn_fwd_splitkv(sp, stream), "b200attn_fwd_splitkv")
+    return o, L
+
+
+def flash_attention_split_kv(q, k, v, causal=False, sm_scale=None):
+    """Forward-only attention over split keys/values ("flash decoding"): same arguments, checks and
+    result as the reference operator (``split_kv.py:282-347``); the result has ``q``'s dtype
+    whatever the split count. Not differentiable, like the reference's."""
+    Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
+    assert Dq == Dk == Dv
+    assert Dk in _SUPPORTED_HEAD_DIMS
+    B, H, M, D = q.shape
+    Hk, Hv = k.shape[1], v.shape[1]
+    assert Hk == Hv, "num of heads in k and v should be equal"
+    assert H % Hk == 0, "number of heads in q must be a multiple of that in k & v"
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("flash_attention_split_kv runs on CUDA tensors only (no CPU fallback)")
+    if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("q, k, v must share dtype float16 or bfloat16")
+    if not (q.device == k.device == v.device):
+        raise ValueError("q, k, v must live on the same device")
+    if k.shape[0] != B or v.shape[0] != B or v.shape[2] != k.shape[2]:
+        raise ValueError("batch / sequence sizes of q, k, v are inconsistent")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    q, k, v = _tma_ready(q.detach()), _tma_ready(k.detach()), _tma_ready(v.detach())
+    lib = _lib.load()
+    device = q.device
+    with torch.cuda.device(device):
+        o, _ = _split_kv_forward(lib, q, k, v, bool(causal), float(sm_scale), _sm_count(device),
+                                 _lib.current_stream_ptr(device), _status_word(device))
+    return o
+
+
 class FlashAttentionFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, sm_scale, dropout_p, return_log_normalizer,
@@ -95,24 +165,19 @@ class FlashAttentionFunction(torch.autograd.Function):
                 seed, offset = reserve_philox_stream(B * H * M * N, device)
             else:
                 seed, offset = 0, 0
-            num_sms = torch.cuda.get_device_properties(device).multi_processor_count
+            num_sms = _sm_count(device)
+            # The reference's rule decides WHETHER the call takes the split-KV branch (and with it
+            # the branch's no-dropout restriction, flash.py:73-77); how many splits this library
+            # then uses is its own tuning and does not change the result.
             num_splits = choose_num_splits(B, H, M, N, num_sms)
             stream = _lib.current_stream_ptr(device)
             status = _status_word(device)
-            L = torch.empty((B, H, M), device=device, dtype=torch.float32)
             if num_splits > 1:
                 assert not is_dropout, "Cannot apply dropout with splitkv."
-                o = torch.empty_like(q)
-                o = o if _tma_ready(o) is o else torch.empty(q.shape, dtype=q.dtype, device=device)
-                part_o = torch.empty((B, H, num_splits, M, D), dtype=torch.float32, device=device)
-                part_l = torch.empty((B, H, num_splits, M), dtype=torch.float32, device=device)
-                sp = _lib.SplitKVParams(
-                    _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o),
-                    L.data_ptr(), part_o.data_ptr(), part_l.data_ptr(),
-                    B, H, Hk, M, N, D, num_splits, _lib.dtype_code(q.dtype), int(bool(causal)),
-                    float(sm_scale), status.data_ptr())
-                _lib.check(lib.b200attn_fwd_splitkv(sp, stream), "b200attn_fwd_splitkv")
+                o, L = _split_kv_forward(lib, q, k, v, bool(causal), float(sm_scale), num_sms, stream,
+                                         status)
             else:
+                L = torch.empty((B, H, M), device=device, dtype=torch.float32)
                 # Backward's row statistic is dot(O, dO): keep the fp32 O for bf16 dropout gradients,
                 # as the reference does (flash.py:86-90).
                 out_dtype = (torch.float32 if is_dropout and q.dtype == torch.bfloat16

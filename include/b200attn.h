@@ -162,6 +162,16 @@ typedef struct {
 
 int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stream);
 
+/* Split count this library prefers for b200attn_fwd_splitkv on the current device (num_sms <= 0:
+ * ask the device). Plays the role of `num_splits_herustic` (split_kv.py:245-278) for the public
+ * `flash_attention_split_kv` (split_kv.py:282-347), but is tuned to this library's kernels: shapes
+ * with at most 4 query rows per KV head (heads per group x M) run a register-resident streaming
+ * kernel with several light CTAs per SM; grouped heads with up to 128 rows per KV head share one
+ * tensor-core tile per KV head; everything else uses one tile pair per query head. The result of
+ * the attention does not depend on the split count beyond fp32 rounding. Returns >= 1. */
+int b200attn_splitkv_num_splits(int32_t B, int32_t Hq, int32_t Hkv, int32_t M, int32_t N, int32_t D,
+                                int32_t num_sms);
+
 /* Merge of two partial attention results over disjoint key sets, in place on the accumulator:
  * lse = log(exp(lse_acc) + exp(lse_part)), o_acc = o_acc*exp(lse_acc-lse) + o_part*exp(lse_part-lse).
  * Both sides are contiguous fp32 arrays [heads, rows_per_head, D] (o) and [heads, rows_per_head]
