@@ -189,6 +189,10 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
     set_error("fwd_splitkv: null output / scratch pointer");
     return B200ATTN_EINVAL;
   }
+  if (reinterpret_cast<uintptr_t>(p->part_o) % 16 != 0) {
+    set_error("fwd_splitkv: part_o must be 16-byte aligned");
+    return B200ATTN_EINVAL;
+  }
   const int n_blocks = cdiv(p->N, 128);
   const int S = p->num_splits < n_blocks ? p->num_splits : n_blocks;
   if (static_cast<int64_t>(p->B) * p->Hq * cdiv(p->M, 256) * p->num_splits > 2147483647ll) {

@@ -79,14 +79,19 @@ def _split_kv_forward(lib, q, k, v, causal, sm_scale, num_sms, stream, status):
     device = q.device
     S = int(lib.b200attn_splitkv_num_splits(B, H, Hk, M, N, D, num_sms))
     o = torch.empty((B, H, M, D), dtype=q.dtype, device=device)
-    L = torch.empty((B, H, M), device=device, dtype=torch.float32)
+    rows = B * H * M
     if S > 1:
-        part_o = torch.empty((B, H, S, M, D), dtype=torch.float32, device=device)
-        part_l = torch.empty((B, H, S, M), dtype=torch.float32, device=device)
-        part_o_ptr, part_l_ptr = part_o.data_ptr(), part_l.data_ptr()
+        # one fp32 allocation: per-split outputs (16-byte aligned rows) | per-split normalisers |
+        # log-normaliser
+        buf = torch.empty(rows * (S * D + S + 1), dtype=torch.float32, device=device)
+        part_o_ptr = buf.data_ptr()
+        part_l_ptr = part_o_ptr + 4 * rows * S * D
+        L = buf[rows * (S * D + S):].view(B, H, M)
     elif (H // Hk) * M <= 2:
+        L = torch.empty((B, H, M), device=device, dtype=torch.float32)
         part_o_ptr = part_l_ptr = L.data_ptr()  # unused by the single-split streaming kernel
     else:
+        L = torch.empty((B, H, M), device=device, dtype=torch.float32)
         fp = _lib.FwdParams(
             _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), L.data_ptr(),
             B, H, Hk, M, N, D, _lib.dtype_code(q.dtype), _lib.dtype_code(q.dtype),
@@ -122,12 +127,17 @@ def flash_attention_split_kv(q, k, v, causal=False, sm_scale=None):
         raise ValueError("batch / sequence sizes of q, k, v are inconsistent")
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
-    q, k, v = _tma_ready(q.detach()), _tma_ready(k.detach()), _tma_ready(v.detach())
+    q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
     lib = _lib.load()
     device = q.device
-    with torch.cuda.device(device):
-        o, _ = _split_kv_forward(lib, q, k, v, bool(causal), float(sm_scale), _sm_count(device),
-                                 _lib.current_stream_ptr(device), _status_word(device))
+    with torch.no_grad():
+        if device.index == torch.cuda.current_device():
+            o, _ = _split_kv_forward(lib, q, k, v, bool(causal), float(sm_scale), _sm_count(device),
+                                     _lib.current_stream_ptr(device), _status_word(device))
+        else:
+            with torch.cuda.device(device):
+                o, _ = _split_kv_forward(lib, q, k, v, bool(causal), float(sm_scale), _sm_count(device),
+                                         _lib.current_stream_ptr(device), _status_word(device))
     return o
 
 

@@ -1,13 +1,14 @@
-"""Registers this implementation as the reference's ``flash_attention`` through the reference's
-own operator registry.
+"""Registers this implementation as the reference's ``flash_attention`` and
+``flash_attention_split_kv`` through the reference's own operator registry.
 
 The reference resolves every public operator by name: ``flag_attn.__getattr__``
 (``src/flag_attn/__init__.py:123-135``) calls ``runtime.backend.resolve_operator``
 (``runtime/backend/op_registry.py:44-60``), which looks the name up in the detected vendor
 package's ``_OPERATOR_EXPORTS`` table (``op_registry.py:19-35``) and falls back to the generic
-Triton implementation. ``install()`` adds one row to the NVIDIA vendor package's table, drops the
-registry's caches and the facade's cached callable, after which ``flag_attn.flash_attention`` is
-this package's function. A declared override that fails to import is an error there, not a
+Triton implementation. ``install()`` adds one row per operator to the NVIDIA vendor package's
+table, drops the registry's caches and the facade's cached callables, after which
+``flag_attn.flash_attention`` and ``flag_attn.flash_attention_split_kv`` are this package's
+functions. A declared override that fails to import is an error there, not a
 fallback, which matches this package having no fallback either.
 """
 from __future__ import annotations
@@ -17,6 +18,10 @@ import sys
 
 OPERATOR = "flash_attention"
 TARGET = ("flagattention_b200.flash", "flash_attention")
+OPERATORS = {
+    OPERATOR: TARGET,
+    "flash_attention_split_kv": ("flagattention_b200.flash", "flash_attention_split_kv"),
+}
 
 
 def _vendor_package(vendor: str):
@@ -31,16 +36,18 @@ def _drop_caches():
             fn.cache_clear()
     facade = sys.modules.get("flag_attn")
     if facade is not None:
-        facade.__dict__.pop(OPERATOR, None)
+        for name in OPERATORS:
+            facade.__dict__.pop(name, None)
 
 
 def install(vendor: str = "nvidia") -> None:
-    """Make ``flag_attn.flash_attention`` resolve to ``flagattention_b200.flash_attention``."""
+    """Make ``flag_attn.flash_attention`` and ``flag_attn.flash_attention_split_kv`` resolve to
+    this package's functions."""
     pkg = _vendor_package(vendor)
     exports = dict(vars(pkg).get("_OPERATOR_EXPORTS", {}))
-    exports[OPERATOR] = TARGET
+    exports.update(OPERATORS)
     pkg._OPERATOR_EXPORTS = exports
-    generic_only = tuple(n for n in vars(pkg).get("_GENERIC_ONLY_OPS", ()) if n != OPERATOR)
+    generic_only = tuple(n for n in vars(pkg).get("_GENERIC_ONLY_OPS", ()) if n not in OPERATORS)
     pkg._GENERIC_ONLY_OPS = generic_only
     _drop_caches()
 
@@ -49,6 +56,7 @@ def uninstall(vendor: str = "nvidia") -> None:
     """Undo ``install()``: the reference's generic implementation is selected again."""
     pkg = _vendor_package(vendor)
     exports = dict(vars(pkg).get("_OPERATOR_EXPORTS", {}))
-    exports.pop(OPERATOR, None)
+    for name in OPERATORS:
+        exports.pop(name, None)
     pkg._OPERATOR_EXPORTS = exports
     _drop_caches()

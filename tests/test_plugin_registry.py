@@ -15,7 +15,8 @@ def fake_flag_attn(tmp_path, monkeypatch):
     (root / "__init__.py").write_text(textwrap.dedent('''
         import importlib
         from . import runtime
-        _OPERATOR_EXPORTS = {"flash_attention": ("flag_attn.flash", "attention")}
+        _OPERATOR_EXPORTS = {"flash_attention": ("flag_attn.flash", "attention"),
+                             "flash_attention_split_kv": ("flag_attn.split_kv", "attention")}
         def __getattr__(name):
             module_name, attribute_name = _OPERATOR_EXPORTS[name]
             value = runtime.backend.resolve_operator(name, module_name, attribute_name)
@@ -23,6 +24,7 @@ def fake_flag_attn(tmp_path, monkeypatch):
             return value
     '''))
     (root / "flash.py").write_text("def attention(*a, **k):\n    return 'generic'\n")
+    (root / "split_kv.py").write_text("def attention(*a, **k):\n    return 'generic-split'\n")
     (root / "runtime" / "__init__.py").write_text(textwrap.dedent('''
         from . import backend
         class _Dev:
@@ -58,10 +60,13 @@ def fake_flag_attn(tmp_path, monkeypatch):
 
 
 def test_install_and_uninstall(fake_flag_attn):
-    from flagattention_b200 import flash_attention, plugin
+    from flagattention_b200 import flash_attention, flash_attention_split_kv, plugin
     fa = fake_flag_attn
     assert fa.flash_attention() == "generic"
+    assert fa.flash_attention_split_kv() == "generic-split"
     plugin.install()
     assert fa.flash_attention is flash_attention
+    assert fa.flash_attention_split_kv is flash_attention_split_kv
     plugin.uninstall()
     assert fa.flash_attention() == "generic"
+    assert fa.flash_attention_split_kv() == "generic-split"
