@@ -18,6 +18,9 @@ _DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
 
 ERROR_NAMES = {0: "OK", -1: "EINVAL", -2: "EUNSUPPORTED", -3: "ECUDA", -4: "ETIMEOUT"}
 
+# Stage bits of b200attn_bwd_stages (include/b200attn.h).
+BWD_STAGE_PREP, BWD_STAGE_KV, BWD_STAGE_Q, BWD_STAGE_ALL, BWD_STAGE_UNFUSED = 1, 2, 4, 7, 8
+
 
 class Tensor4(Structure):
     _fields_ = [("ptr", c_void_p), ("stride", c_int64 * 4)]

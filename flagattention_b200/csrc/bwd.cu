@@ -12,8 +12,8 @@ static int pad128(int m) { return (m + 127) / 128 * 128; }
 static long long* g_trace_dev = nullptr;
 static long long* trace_buffer() {
   if (g_trace_dev == nullptr) {
-    cudaMalloc(&g_trace_dev, sizeof(long long) * 2 * 8192);
-    cudaMemset(g_trace_dev, 0, sizeof(long long) * 2 * 8192);
+    cudaMalloc(&g_trace_dev, sizeof(long long) * 4 * 8192);
+    cudaMemset(g_trace_dev, 0, sizeof(long long) * 4 * 8192);
   }
   return g_trace_dev;
 }
@@ -77,6 +77,33 @@ static int dispatch(int D, const BwdLaunch& L) {
   }
 }
 
+// FUSED path: dQ = sm_scale * accumulator, rounded to the 16-bit output. 8 elements per thread.
+template <bool BF16>
+__global__ void dq_convert_kernel(const float* __restrict__ acc, uint16_t* __restrict__ dq, int64_t sb,
+                                  int64_t sh, int64_t sr, int Hq, int M, int D, float scale, int64_t n_vec) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = i * 8;
+    const int d = static_cast<int>(e % D);
+    const int64_t row = e / D;
+    const int m = static_cast<int>(row % M);
+    const int64_t bh = row / M;
+    const int h = static_cast<int>(bh % Hq);
+    const int64_t b = bh / Hq;
+    const float4 x = *reinterpret_cast<const float4*>(acc + e);
+    const float4 y = *reinterpret_cast<const float4*>(acc + e + 4);
+    uint4 v;
+    v.x = pack2<BF16>(x.x * scale, x.y * scale);
+    v.y = pack2<BF16>(x.z * scale, x.w * scale);
+    v.z = pack2<BF16>(y.x * scale, y.y * scale);
+    v.w = pack2<BF16>(y.z * scale, y.w * scale);
+    *reinterpret_cast<uint4*>(dq + b * sb + h * sh + static_cast<int64_t>(m) * sr + d) = v;
+  }
+}
+
+// Whether the backward of this head dimension produces dQ inside the dK/dV pass.
+static bool fused_dq(int D, int stages) { return D == 128 && !(stages & B200ATTN_BWD_STAGE_UNFUSED); }
+
 template <int D>
 static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t stream, int stages) {
   BwdLaunch kv, qq;
@@ -127,6 +154,31 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
   qq.mode = MODE_Q;
   qq.stream = stream;
 
+  if (fused_dq(D, stages)) {
+    // One pass for dK, dV and dQ; the fp32 dQ accumulator sits behind the statistics in the workspace.
+    float* dq_acc = reinterpret_cast<float*>(stats + static_cast<size_t>(p->B) * p->Hq * a.Mpad);
+    const int64_t n_acc = static_cast<int64_t>(p->B) * p->Hq * p->M * D;
+    if (stages & B200ATTN_BWD_STAGE_KV) {
+      B200ATTN_CUDA_OK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(n_acc) * sizeof(float), stream));
+      kv.fused = true;
+      kv.args.dq_acc = dq_acc;
+      if ((rc = dispatch(D, kv))) return rc;
+    }
+    if (stages & B200ATTN_BWD_STAGE_Q) {
+      const int64_t n_vec = n_acc / 8;
+      const unsigned blocks = static_cast<unsigned>(n_vec / 256 + 1 < 148 * 16 ? n_vec / 256 + 1 : 148 * 16);
+      uint16_t* out = static_cast<uint16_t*>(p->dq.ptr);
+      if (kv.bf16) {
+        dq_convert_kernel<true><<<blocks, 256, 0, stream>>>(dq_acc, out, p->dq.stride[0], p->dq.stride[1],
+                                                           p->dq.stride[2], p->Hq, p->M, D, p->sm_scale, n_vec);
+      } else {
+        dq_convert_kernel<false><<<blocks, 256, 0, stream>>>(dq_acc, out, p->dq.stride[0], p->dq.stride[1],
+                                                            p->dq.stride[2], p->Hq, p->M, D, p->sm_scale, n_vec);
+      }
+      B200ATTN_CUDA_OK(cudaGetLastError());
+    }
+    return B200ATTN_OK;
+  }
   if ((stages & B200ATTN_BWD_STAGE_KV) && (rc = dispatch(D, kv))) return rc;
   if ((stages & B200ATTN_BWD_STAGE_Q) && (rc = dispatch(D, qq))) return rc;
   return B200ATTN_OK;
@@ -169,9 +221,12 @@ static int run_total(const b200attn_total_params* p, float2* stats, cudaStream_t
 
 extern "C" size_t b200attn_bwd_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t M, int32_t N,
                                                int32_t D) {
-  (void)Hkv; (void)N; (void)D;
+  (void)Hkv; (void)N;
   if (B <= 0 || Hq <= 0 || M <= 0) return 0;
-  return static_cast<size_t>(B) * Hq * b200attn::pad128(M) * sizeof(float2);
+  size_t bytes = static_cast<size_t>(B) * Hq * b200attn::pad128(M) * sizeof(float2);
+  // D = 128: fp32 dQ accumulator of the fused pass behind the statistics
+  if (D == 128) bytes += static_cast<size_t>(B) * Hq * M * D * sizeof(float);
+  return bytes;
 }
 
 extern "C" size_t b200attn_total_workspace_bytes(int32_t B, int32_t Hq, int32_t M) {
@@ -325,6 +380,6 @@ extern "C" int b200attn_total_attention_static(const b200attn_total_params* p, v
 // Developer build only: copies the clock64() stamps of the last backward-family launch.
 extern "C" int b200attn_debug_read_trace(long long* host_buf) {
   if (b200attn::g_trace_dev == nullptr) return -1;
-  return cudaMemcpy(host_buf, b200attn::g_trace_dev, sizeof(long long) * 2 * 8192, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -3;
+  return cudaMemcpy(host_buf, b200attn::g_trace_dev, sizeof(long long) * 4 * 8192, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -3;
 }
 #endif

@@ -21,6 +21,17 @@
 // (T1, T2) buffers of 64+64 fp32 columns; P / dS overwrite T1 as packed 16-bit pairs and are
 // consumed from TMEM as the A operand of the accumulating MMAs.
 //
+// FUSED (MODE_KV, D = 128 only): the same pass also produces dQ, so P and dS are computed once for
+// the whole backward. The softmax groups leave dS^T a second time in shared memory ([128 keys x 64
+// queries], 128-byte swizzled rows); the MMA warp forms dQ^T = K^T dS^T (A = the resident K tile read
+// MN-major, 128 x 64 fp32) in the step's dead T2 columns, ahead of the step's accumulating products
+// so that the read-back overlaps them; four extra warps read it back, transpose it through two
+// 16 KB staging tiles ([32 queries][128 features] fp32, the layout of the accumulator rows) and add
+// it to an fp32 dQ accumulator in global memory with cp.reduce.async.bulk (.add.f32), since every
+// key block contributes to every query row. A conversion kernel scales and rounds the accumulator
+// afterwards. The reductions (32 KB per step and SM) run at the rate the L2 accepts them, about
+// 13 bytes per clock and SM, which is what bounds this pass.
+//
 // Per-query statistics come from a padded scratch array holding, per pair of queries, the float4
 // (-lse[m]*log2e, -lse[m+1]*log2e, -delta[m], -delta[m+1]); it is padded to a multiple of 128
 // queries with (-inf, 0) so that padded and key-less queries contribute exactly zero. The pair
@@ -54,31 +65,38 @@ struct BwdArgs {
   float sm_scale, qk_scale;
   DropoutCtx drop;
   int32_t* status;
+  float* dq_acc;        // FUSED: [B, Hq, M, D] fp32, zero before the launch
 #ifdef B200ATTN_TIMING
   long long* trace;
 #endif
 };
 
-template <int D, int MODE>
+template <int D, int MODE, bool FUSED = false>
 struct BwdSmem {
-  static constexpr int STAGES = 4;
+  static constexpr int STAGES = FUSED ? 3 : 4;
   static constexpr int N_A = MODE == MODE_TOTAL ? 1 : 2;       // resident tiles
   static constexpr int N_B = MODE == MODE_TOTAL ? 1 : 2;       // streamed tiles per stage
   static constexpr int A_BYTES = N_A * TileCfg<D>::TILE_BYTES; // 128 x D each
   static constexpr int B_TILE_BYTES = 64 * D * 2;
   static constexpr int STATS_BYTES = MODE == MODE_Q ? 0 : 512; // 64 x float2
   static constexpr int STAGE_BYTES = N_B * B_TILE_BYTES + 1024; // tiles + stats slot (keeps 1 KB alignment)
-  static constexpr int BAR_OFFSET = A_BYTES + STAGES * STAGE_BYTES;
+  static constexpr int DS_TILE_BYTES = 128 * 128;               // FUSED: dS^T, 128 keys x 64 queries
+  static constexpr int DS_OFFSET = A_BYTES + STAGES * STAGE_BYTES;
+  static constexpr int DQ_STAGE_BYTES = 32 * D * 4;             // FUSED: 32 queries x D fp32 of dQ on its way out
+  static constexpr int DQ_STAGE_OFFSET = DS_OFFSET + (FUSED ? DS_TILE_BYTES : 0);
+  static constexpr int BAR_OFFSET = DQ_STAGE_OFFSET + (FUSED ? 2 * DQ_STAGE_BYTES : 0);
   static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;
+  static constexpr int THREADS = FUSED ? 448 : 320;
 };
 
-template <int D, bool BF16, bool DROPOUT, int MODE>
-__global__ void __launch_bounds__(320, 1)
+template <int D, bool BF16, bool DROPOUT, int MODE, bool FUSED = false>
+__global__ void __launch_bounds__((BwdSmem<D, MODE, FUSED>::THREADS), 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
            const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
            const BwdArgs args) {
   using Cfg = TileCfg<D>;
-  using Sm = BwdSmem<D, MODE>;
+  using Sm = BwdSmem<D, MODE, FUSED>;
+  static_assert(!FUSED || (MODE == MODE_KV && D == 128), "the fused dQ pass exists for MODE_KV, D = 128");
   constexpr int STAGES = Sm::STAGES;
   constexpr int STEP = 64;                                  // columns per step
   constexpr int CHUNK_BYTES_B = STEP * Cfg::ROW_BYTES;      // one [64 x CHUNK] box
@@ -103,7 +121,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
   uint64_t* t_full = b_empty + STAGES;     // [2]
   uint64_t* p_ready = t_full + 2;          // [2]
   uint64_t* acc_full = p_ready + 2;        // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* dq_ready = acc_full + 1;       // [2] FUSED: dQ^T of the step is complete in TMEM
+  uint64_t* dq_drained = dq_ready + 2;     // [2] FUSED: ... and has been read back
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 2);
+  uint8_t* sDS = smem + Sm::DS_OFFSET;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -149,6 +170,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
     for (int i = 0; i < 2; ++i) {
       mbar_init(&t_full[i], 1);
       mbar_init(&p_ready[i], 256);
+      mbar_init(&dq_ready[i], 1);
+      mbar_init(&dq_drained[i], 128);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -281,6 +304,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           mma_ts_w(d, a + (s >> 1) * 32 + (s & 1) * 8, db + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_ACC,
                    (accumulate || s > 0) ? 1u : 0u);
       };
+      // FUSED: dQ^T (128 feature rows x 64 queries) = K^T dS^T into the T2 columns of buffer `buf`.
+      auto issue_dq = [&](int buf) {
+        constexpr uint32_t IDESC_DQ = make_idesc(BF16, 128, STEP, true, true);
+        constexpr uint64_t DS_DESC = make_smem_desc_hi(Sm::DS_TILE_BYTES, 1024, SWZ_128B);
+        const uint64_t da = smem_desc(Cfg::MNMAJOR_DESC, a_addr);  // K, rows = contraction index
+        const uint64_t db = smem_desc(DS_DESC, smem_u32(sDS));
+#pragma unroll
+        for (int s = 0; s < 128 / 16; ++s)
+          mma_ss_w(tmem_base + BUF_BASE + buf * 128 + 64, da + ((s * 16 * Cfg::ROW_BYTES) >> 4),
+                   db + ((s * 16 * 128) >> 4), IDESC_DQ, s > 0 ? 1u : 0u);
+      };
       bool ok = true;
       if (!wait(a_full, 0)) { fail(ST_WAIT_TMA); ok = false; }
       if (ok && !wait(&b_full[0], 0)) { fail(ST_WAIT_TMA); ok = false; }
@@ -299,6 +333,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           B200ATTN_STAMP(1, 4 * i + 0);
           const bool w = wait(&b_full[st_next], ((i + 1) / STAGES) & 1);
           if (!__all_sync(0xffffffffu, w)) { fail(ST_WAIT_TMA); ok = false; break; }
+          if constexpr (FUSED) {
+            // the T2 columns of the other buffer still hold dQ^T of step i - 1 until it is read back
+            if (i >= 1) {
+              B200ATTN_STAMP(3, 2 * i + 0);
+              const bool w2 = wait(&dq_drained[buf ^ 1], ((i - 1) >> 1) & 1);
+              B200ATTN_STAMP(3, 2 * i + 1);
+              if (!__all_sync(0xffffffffu, w2)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+            }
+          }
           tc_fence_after();
           B200ATTN_STAMP(1, 4 * i + 1);
           issue_t(buf ^ 1, st_next);
@@ -312,6 +355,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         tc_fence_after();
         B200ATTN_STAMP(1, 4 * i + 3);
         if constexpr (MODE == MODE_KV) {
+          if constexpr (FUSED) {
+            // first, so that its read-back overlaps the two accumulating products and the T2
+            // columns are free again when the next T products are issued
+            issue_dq(buf);
+            tc_commit_w(&dq_ready[buf]);
+          }
           issue_acc(1, buf, 0, st, 1, i > 0);  // dV += P^T  dO
           issue_acc(0, buf, 1, st, 0, i > 0);  // dK += dS^T Q
         } else if constexpr (MODE == MODE_Q) {
@@ -322,6 +371,59 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       if (ok) tc_commit_w(acc_full);
     }
     __syncwarp();
+  } else if (warp >= 10) {
+    // ------------------------------------------------- FUSED: dQ^T read-back and global reduction
+    if constexpr (FUSED) {
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      const int d = (warp & 3) * 32 + lane;  // feature index = TMEM lane
+      for (int i = 0; i < T; ++i) {
+        const int buf = i & 1;
+        const int hh = i / steps_per_head;
+        const int col = col_lo + (i - hh * steps_per_head) * STEP;
+        if (warp == 10) B200ATTN_STAMP(2, 4 * i + 0);
+        {
+          const bool w = wait(&dq_ready[buf], (i >> 1) & 1);
+          if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); break; }
+        }
+        if (warp == 10) B200ATTN_STAMP(2, 4 * i + 1);
+        tc_fence_after();
+        uint32_t v[STEP];
+        tmem_ld32(tmem_base + lane_base + BUF_BASE + buf * 128 + 64, v);
+        tmem_ld32(tmem_base + lane_base + BUF_BASE + buf * 128 + 96, v + 32);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&dq_drained[buf]);
+        if (warp == 10) B200ATTN_STAMP(2, 4 * i + 2);
+        // Out through shared memory, 32 queries at a time: the tile is laid out like the
+        // accumulator rows ([query][feature], contiguous in global memory) and one bulk
+        // reduction adds it to the fp32 accumulator.
+        float* dst = args.dq_acc + ((static_cast<int64_t>(b) * args.Hq + h_first + hh) * args.M + col) * D;
+        const int n_valid = min(STEP, args.M - col);
+        float* stage0 = reinterpret_cast<float*>(smem + Sm::DQ_STAGE_OFFSET);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int rows_out = min(32, n_valid - half * 32);
+          // two staging tiles: this one was last read by the reduction issued two halves ago
+          if (threadIdx.x == 320) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          float* stage = stage0 + half * (Sm::DQ_STAGE_BYTES / 4);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) stage[c * D + d] = __uint_as_float(v[half * 32 + c]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          if (threadIdx.x == 320 && rows_out > 0) {
+            asm volatile(
+                "cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                ::"l"(dst + half * 32 * D), "r"(smem_u32(stage)), "r"(rows_out * D * 4)
+                : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        if (warp == 10) B200ATTN_STAMP(2, 4 * i + 3);
+      }
+      // the staging tile must outlive the reductions that read it
+      if (threadIdx.x == 320) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
   } else {
     // --------------------------------------------------------- softmax groups
     const int wg = warp >> 2;
@@ -352,7 +454,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       const int col0 = col_lo + (i - hh * steps_per_head) * STEP + wg * HALF;  // first column of this group
       const int h = h_first + hh;
       const uint32_t t1_addr = tmem_base + lane_base + BUF_BASE + buf * 128;
-      if (warp == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 0);
+      if (warp == 0) B200ATTN_STAMP(0, 4 * i + 0);
       // Dropout decisions for this thread's 32 (row, column) pairs of the step, generated before the
       // T products are awaited so the integer work overlaps the tensor core.
       uint32_t keep_bits = 0xffffffffu;
@@ -370,13 +472,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
       }
       tc_fence_after();
-      if (warp == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 1);
+      if (warp == 0) B200ATTN_STAMP(0, 4 * i + 1);
       uint32_t t1[HALF];
       uint32_t t2[MODE == MODE_TOTAL ? 1 : HALF];
       tmem_ld32(t1_addr + wg * HALF, t1);
       if constexpr (MODE != MODE_TOTAL) tmem_ld32(t1_addr + 64 + wg * HALF, t2);
       tmem_wait_ld();
-      if (warp == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 2);
+      if (warp == 0) B200ATTN_STAMP(0, 4 * i + 2);
 
       // Does this step cross the causal boundary for some row of the block?
       bool diag = false;
@@ -440,11 +542,28 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         // never touch each other's unread inputs.
         if constexpr (MODE == MODE_KV) tmem_st16(t1_addr + wg * HALF, t1);
         tmem_st16(t1_addr + wg * HALF + 16, t2);
+        if constexpr (FUSED) {
+          // dS^T once more, as the shared-memory B operand of dQ^T: row = key, 64 queries = 128
+          // bytes, 16-byte chunks permuted by the 128-byte swizzle.
+          // (one tile: the product that read the previous step's copy must have completed)
+          if (i >= 1) {
+            const bool w = wait(&dq_ready[buf ^ 1], ((i - 1) >> 1) & 1);
+            if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
+          }
+          uint8_t* ds_row = sDS + row_local * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int chunk = (wg * 4 + j) ^ (row_local & 7);
+            *reinterpret_cast<uint4*>(ds_row + chunk * 16) =
+                make_uint4(t2[4 * j + 0], t2[4 * j + 1], t2[4 * j + 2], t2[4 * j + 3]);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
         tmem_wait_st();
       }
       tc_fence_before();
       mbar_arrive(&p_ready[buf]);
-      if (warp == 0) B200ATTN_STAMP(0, 4 * (i >> 1) + 3);
+      if (warp == 0) B200ATTN_STAMP(0, 4 * i + 3);
     }
 
     // ------------------------------------------------------------- epilogue

@@ -10,14 +10,15 @@ struct BwdLaunch {
   BwdArgs args;
   dim3 grid;
   bool bf16, dropout;
+  bool fused = false;  // MODE_KV, D = 128: dQ produced in the same pass (args.dq_acc)
   int mode;
   cudaStream_t stream;
 };
 
-template <int D, bool BF16, bool DROPOUT, int MODE>
+template <int D, bool BF16, bool DROPOUT, int MODE, bool FUSED = false>
 int launch_bwd_variant(const BwdLaunch& L) {
-  auto kernel = bwd_kernel<D, BF16, DROPOUT, MODE>;
-  constexpr int smem = BwdSmem<D, MODE>::TOTAL;
+  auto kernel = bwd_kernel<D, BF16, DROPOUT, MODE, FUSED>;
+  constexpr int smem = BwdSmem<D, MODE, FUSED>::TOTAL;
   static bool attr_done[64] = {};
   int dev = 0;
   B200ATTN_CUDA_OK(cudaGetDevice(&dev));
@@ -25,7 +26,7 @@ int launch_bwd_variant(const BwdLaunch& L) {
     B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
-  kernel<<<L.grid, 320, smem, L.stream>>>(L.tmA1, L.tmA2, L.tmB1, L.tmB2, L.args);
+  kernel<<<L.grid, BwdSmem<D, MODE, FUSED>::THREADS, smem, L.stream>>>(L.tmA1, L.tmA2, L.tmB1, L.tmB2, L.args);
   B200ATTN_CUDA_OK(cudaGetLastError());
   return B200ATTN_OK;
 }
@@ -35,6 +36,12 @@ int launch_bwd_d(const BwdLaunch& L) {
   if (L.mode == MODE_TOTAL) {
     return L.bf16 ? launch_bwd_variant<D, true, false, MODE_TOTAL>(L)
                   : launch_bwd_variant<D, false, false, MODE_TOTAL>(L);
+  }
+  if constexpr (D == 128) {
+    if (L.mode == MODE_KV && L.fused) {
+      if (L.bf16) return L.dropout ? launch_bwd_variant<D, true, true, MODE_KV, true>(L) : launch_bwd_variant<D, true, false, MODE_KV, true>(L);
+      return L.dropout ? launch_bwd_variant<D, false, true, MODE_KV, true>(L) : launch_bwd_variant<D, false, false, MODE_KV, true>(L);
+    }
   }
   if (L.mode == MODE_KV) {
     if (L.bf16) return L.dropout ? launch_bwd_variant<D, true, true, MODE_KV>(L) : launch_bwd_variant<D, true, false, MODE_KV>(L);

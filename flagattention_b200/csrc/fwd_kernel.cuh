@@ -84,6 +84,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 static constexpr float RESCALE_THRESHOLD = 8.0f;
 
+// Which of every 8 consecutive column pairs compute their exponential with the polynomial on the
+// FMA pipe instead of ex2.approx on the special-function unit (bit k = pair k).
+#ifndef B200ATTN_FWD_POLY_MASK
+#define B200ATTN_FWD_POLY_MASK 0x00u
+#endif
+static constexpr uint32_t POLY_MASK = B200ATTN_FWD_POLY_MASK;
+
 template <int D, bool BF16, bool DROPOUT>
 __global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -450,6 +457,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
       const float m_eff = (m_run == -INFINITY) ? 0.f : m_run;
       const float neg_ms = -m_eff * qk_scale;
+      const uint64_t scale2 = f2_pack(qk_scale, qk_scale), neg_ms2 = f2_pack(neg_ms, neg_ms);
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
       // P goes back to TMEM in two halves of 64 keys so that the P V product can start on the
       // first half while the second is still being exponentiated.
@@ -457,10 +465,22 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       for (int half = 0; half < 2; ++half) {
 #pragma unroll
         for (int i = half * 64; i < half * 64 + 64; i += 4) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), qk_scale, neg_ms));
-          float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_ms));
-          float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, neg_ms));
-          float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, neg_ms));
+          float p0, p1, p2, p3;
+          // A fixed subset of the column pairs takes the polynomial route (see POLY_MASK).
+          if ((POLY_MASK >> ((i >> 1) & 7)) & 1u) {
+            exp2_poly_pair(f2_fma(f2_pack(__uint_as_float(s[i + 0]), __uint_as_float(s[i + 1])), scale2, neg_ms2),
+                           p0, p1);
+          } else {
+            p0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), qk_scale, neg_ms));
+            p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_ms));
+          }
+          if ((POLY_MASK >> (((i >> 1) + 1) & 7)) & 1u) {
+            exp2_poly_pair(f2_fma(f2_pack(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), scale2, neg_ms2),
+                           p2, p3);
+          } else {
+            p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, neg_ms));
+            p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, neg_ms));
+          }
           sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
           if constexpr (DROPOUT) {
             const uint32_t kb = keep_bits[i >> 5] >> (i & 31);

@@ -124,12 +124,16 @@ int b200attn_bwd(const b200attn_bwd_params* p, void* stream);
 
 /* The same backward restricted to some of its stages, so a profiler or benchmark can time the
  * kernels one by one. PREP = delta + statistics preprocess, KV = the dK/dV kernel, Q = the dQ
- * kernel; KV and Q need the scratch PREP wrote. No counterpart in the reference. */
+ * kernel; KV and Q need the scratch PREP wrote. At D = 128 the KV stage is a fused pass that also
+ * accumulates dQ in fp32 (in the workspace, by global reductions, so dQ is reproducible only up to
+ * fp32 summation order) and the Q stage is the conversion of that accumulator; adding UNFUSED
+ * selects the two separate kernels instead. No counterpart in the reference. */
 enum {
   B200ATTN_BWD_STAGE_PREP = 1,
   B200ATTN_BWD_STAGE_KV = 2,
   B200ATTN_BWD_STAGE_Q = 4,
-  B200ATTN_BWD_STAGE_ALL = 7
+  B200ATTN_BWD_STAGE_ALL = 7,
+  B200ATTN_BWD_STAGE_UNFUSED = 8
 };
 int b200attn_bwd_stages(const b200attn_bwd_params* p, void* stream, int32_t stages);
 

@@ -119,6 +119,33 @@ def test_attention_bwd(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
     check_device_status()
 
 
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,scale",
+                         [p for p in _params([s for s in BWD_SHAPES if s[5] == 128])])
+def test_attention_bwd_deterministic_mode(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
+    """Under torch.use_deterministic_algorithms(True) head dimension 128 uses the two separate
+    backward kernels instead of the fused pass with global reductions: same parity rule, and two runs
+    agree bit for bit."""
+    q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, layout, scale, seed=10086, requires_grad=True)
+    o_ref = attention_forward(q, k, v, causal, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
+    o_low = attention_forward(q, k, v, causal, upcast=False)
+    g_low = torch.autograd.grad(o_low, (q, k, v), do)
+    o = flash_attention(q, k, v, causal)
+    g_fused = torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
+    torch.use_deterministic_algorithms(True)
+    try:
+        g = torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
+        g_again = torch.autograd.grad(o, (q, k, v), do)
+    finally:
+        torch.use_deterministic_algorithms(False)
+    for name, a, a2, f, b_, c in zip(("dq", "dk", "dv"), g, g_again, g_fused, g_low, g_ref):
+        assert_2x_rule(name, a, b_, c)
+        assert torch.equal(a, a2)
+        if name != "dq":
+            assert torch.equal(a, f)  # dK and dV do not depend on the choice
+    check_device_status()
+
+
 @pytest.mark.parametrize("B,H,M,N,D,dtype,layout,scale", [
     pytest.param(*s, dt, lay, sc, id=f"{'x'.join(map(str, s))}-{str(dt)[6:]}-{lay}-s{sc:g}")
     for s, (dt, lay, sc) in zip(AUX_SHAPES * 2, itertools.cycle(itertools.product(

@@ -30,7 +30,7 @@ def test_c2_gqa_prefill_train_step():
     q, k, v, do = (_gen(s, dt, i) for i, s in enumerate([(B, Hq, M, D), (B, Hk, N, D), (B, Hk, N, D), (B, Hq, M, D)]))
     q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
     o, lse, _, _, _ = flash_attention(q, k, v, causal=True, return_log_normalizer=True)
-    dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+    dq, dk, dv = torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
     check_device_status()
     # (a) oracle on batch 1, KV group 3 (query heads 12..15): an independent unit of the problem
     b, g = 1, 3
@@ -49,10 +49,21 @@ def test_c2_gqa_prefill_train_step():
     q2, k2, v2 = (t.detach()[b:b + 1, sl].clone().requires_grad_(True)
                   for t, sl in ((q, slice(4 * g, 4 * g + 4)), (k, slice(g, g + 1)), (v, slice(g, g + 1))))
     o2, lse2, _, _, _ = flash_attention(q2, k2, v2, causal=True, return_log_normalizer=True)
-    g2 = torch.autograd.grad(o2, (q2, k2, v2), dos.clone())
+    g2 = torch.autograd.grad(o2, (q2, k2, v2), dos.clone(), retain_graph=True)
     assert torch.equal(o2, o[b:b + 1, 4 * g:4 * g + 4]) and torch.equal(lse2, lse[b:b + 1, 4 * g:4 * g + 4])
-    assert torch.equal(g2[0], dq[b:b + 1, 4 * g:4 * g + 4])
     assert torch.equal(g2[1], dk[b:b + 1, g:g + 1]) and torch.equal(g2[2], dv[b:b + 1, g:g + 1])
+    # dQ at D = 128 is summed over the key blocks by fp32 reductions whose order is not fixed: equal up
+    # to that, and bit for bit when PyTorch's deterministic mode selects the two separate kernels.
+    torch.testing.assert_close(g2[0].float(), dq[b:b + 1, 4 * g:4 * g + 4].float(), atol=2e-3, rtol=2e-2)
+    torch.use_deterministic_algorithms(True)
+    try:
+        d_full = torch.autograd.grad(o, (q, k, v), do)
+        d_part = torch.autograd.grad(o2, (q2, k2, v2), dos.clone())
+    finally:
+        torch.use_deterministic_algorithms(False)
+    assert torch.equal(d_part[0], d_full[0][b:b + 1, 4 * g:4 * g + 4])
+    assert torch.equal(d_full[1], dk) and torch.equal(d_full[2], dv)
+    assert_2x_rule("dq (separate kernels)", d_full[0][b:b + 1, 4 * g:4 * g + 4], g_low[0], rdq)
 
 
 def test_c3_d64_dropout_with_aux_outputs():

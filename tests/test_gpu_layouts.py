@@ -87,6 +87,19 @@ def test_mnmajor_a(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_mnmajor_a_times_mnmajor_b_n64(dtype):
+    """dQ^T = K^T dS^T of the fused backward: both operands stored with the contraction index as
+    the row (K as two 64-column chunks, dS^T as one 128-byte-row tile), N = 64."""
+    dev = torch.device("cuda", 0)
+    bf = dtype == torch.bfloat16
+    am = torch.randn(128, 128, device=dev, dtype=dtype)
+    bm = torch.randn(128, 64, device=dev, dtype=dtype)
+    run(am, bm, am.float().T @ bm.float(), box_cols=64, swizzle=3, a_in_tmem=0, n=64, k_steps=8,
+        idesc=idesc(bf, 128, 64, 1, 1), a_desc_hi=desc_hi(16384, 1024, 2), b_desc_hi=desc_hi(16384, 1024, 2),
+        a_step_bytes=2048, b_step_bytes=2048)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("cols,row_bytes", [(128, 128), (64, 128), (32, 64), (16, 32)])
 def test_tmem_a_filled_by_tcgen05_cp(dtype, cols, row_bytes):
     """A operand staged by TMA in shared memory, moved to TMEM one K=16 slice at a time with
