@@ -170,7 +170,7 @@ def run_step(cfg, q, k, v, do):
 
 def kernels_per_step(cfg) -> int:
     # forward: 1 kernel; backward: delta, statistics, then either the dK/dV kernel and the dQ kernel
-    # or (D = 128) the fused dK/dV/dQ kernel and the dQ conversion (the accumulator's memset is the
+    # or (D = 128 and 64) the fused dK/dV/dQ kernel and the dQ conversion (the accumulator's memset is the
     # driver's, not counted).
     return 1 + (4 if cfg["mode"] == "fwd+bwd" else 0)
 
@@ -216,9 +216,9 @@ def time_kernels(cfg, q, k, v, do, iters=5):
                             lse.data_ptr(), delta.data_ptr(), ws.data_ptr(), B, Hq, Hkv, M, N, D, dt, dt,
                             int(cfg["causal"]), sm_scale, float(cfg["dropout_p"]), 12345, 0,
                             status.data_ptr())
-        # D = 128: one fused pass makes dK, dV and dQ (plus the zeroing of its fp32 dQ accumulator),
+        # D = 128 and 64: one fused pass makes dK, dV and dQ (plus the zeroing of its fp32 dQ accumulator),
         # followed by the accumulator's conversion; other head dimensions run two separate kernels.
-        names = (("bwd_prep_kernels", 1), ("bwd_kernel<kv+dq>", 2), ("dq_convert_kernel", 4)) if D == 128 else \
+        names = (("bwd_prep_kernels", 1), ("bwd_kernel<kv+dq>", 2), ("dq_convert_kernel", 4)) if D in (64, 128) else \
                 (("bwd_prep_kernels", 1), ("bwd_kernel<kv>", 2), ("bwd_kernel<q>", 4))
         for name, mask in names:
             out[name] = timed(lambda m=mask: _lib.check(lib.b200attn_bwd_stages(bp, stream, m), name))
@@ -494,7 +494,7 @@ def main():
         f_fwd = fwd_flops(kcfg)
         # Algorithmic FLOPs per launch: forward 2 GEMMs; dK/dV kernel 4 of the backward's 5 GEMMs
         # (S, dP, dV, dK); dQ kernel 1 (its S and dP are recomputation and not counted).
-        # The fused D = 128 pass performs all 5 (its launch time includes zeroing the dQ accumulator).
+        # The fused pass (D = 128 and 64) performs all 5 (its launch time includes zeroing the dQ accumulator).
         alg = {"fwd_kernel": f_fwd, "bwd_kernel<kv>": 2.0 * f_fwd, "bwd_kernel<q>": 0.5 * f_fwd,
                "bwd_kernel<kv+dq>": 2.5 * f_fwd}
         dominant = max((n for n in kern_ms if n in alg), key=lambda n: kern_ms[n])

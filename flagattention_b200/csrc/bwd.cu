@@ -102,7 +102,7 @@ __global__ void dq_convert_kernel(const float* __restrict__ acc, uint16_t* __res
 }
 
 // Whether the backward of this head dimension produces dQ inside the dK/dV pass.
-static bool fused_dq(int D, int stages) { return D == 128 && !(stages & B200ATTN_BWD_STAGE_UNFUSED); }
+static bool fused_dq(int D, int stages) { return (D == 128 || D == 64) && !(stages & B200ATTN_BWD_STAGE_UNFUSED); }
 
 template <int D>
 static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t stream, int stages) {
@@ -224,8 +224,8 @@ extern "C" size_t b200attn_bwd_workspace_bytes(int32_t B, int32_t Hq, int32_t Hk
   (void)Hkv; (void)N;
   if (B <= 0 || Hq <= 0 || M <= 0) return 0;
   size_t bytes = static_cast<size_t>(B) * Hq * b200attn::pad128(M) * sizeof(float2);
-  // D = 128: fp32 dQ accumulator of the fused pass behind the statistics
-  if (D == 128) bytes += static_cast<size_t>(B) * Hq * M * D * sizeof(float);
+  // D = 128 and 64: fp32 dQ accumulator of the fused pass behind the statistics
+  if (D == 128 || D == 64) bytes += static_cast<size_t>(B) * Hq * M * D * sizeof(float);
   return bytes;
 }
 

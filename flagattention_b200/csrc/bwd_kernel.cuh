@@ -21,10 +21,11 @@
 // (T1, T2) buffers of 64+64 fp32 columns; P / dS overwrite T1 as packed 16-bit pairs and are
 // consumed from TMEM as the A operand of the accumulating MMAs.
 //
-// FUSED (MODE_KV, D = 128 only): the same pass also produces dQ, so P and dS are computed once for
+// FUSED (MODE_KV, D = 128 and 64): the same pass also produces dQ, so P and dS are computed once for
 // the whole backward. The softmax groups leave dS^T a second time in shared memory ([128 keys x 64
 // queries], 128-byte swizzled rows); the MMA warp forms dQ^T = K^T dS^T (A = the resident K tile read
-// MN-major, 128 x 64 fp32) in the step's dead T2 columns, ahead of the step's accumulating products
+// MN-major, 128 x 64 fp32) in the step's dead T2 columns (D = 128) or in columns of its own (D = 64),
+// ahead of the step's accumulating products
 // so that the read-back overlaps them; four extra warps read it back, transpose it through two
 // 16 KB staging tiles ([32 queries][128 features] fp32, the layout of the accumulator rows) and add
 // it to an fp32 dQ accumulator in global memory with cp.reduce.async.bulk (.add.f32), since every
@@ -73,7 +74,7 @@ struct BwdArgs {
 
 template <int D, int MODE, bool FUSED = false>
 struct BwdSmem {
-  static constexpr int STAGES = FUSED ? 3 : 4;
+  static constexpr int STAGES = (FUSED && D == 128) ? 3 : 4;
   static constexpr int N_A = MODE == MODE_TOTAL ? 1 : 2;       // resident tiles
   static constexpr int N_B = MODE == MODE_TOTAL ? 1 : 2;       // streamed tiles per stage
   static constexpr int A_BYTES = N_A * TileCfg<D>::TILE_BYTES; // 128 x D each
@@ -96,7 +97,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
            const BwdArgs args) {
   using Cfg = TileCfg<D>;
   using Sm = BwdSmem<D, MODE, FUSED>;
-  static_assert(!FUSED || (MODE == MODE_KV && D == 128), "the fused dQ pass exists for MODE_KV, D = 128");
+  static_assert(!FUSED || (MODE == MODE_KV && (D == 128 || D == 64)),
+                "the fused dQ pass exists for MODE_KV, D = 128 and 64");
   constexpr int STAGES = Sm::STAGES;
   constexpr int STEP = 64;                                  // columns per step
   constexpr int CHUNK_BYTES_B = STEP * Cfg::ROW_BYTES;      // one [64 x CHUNK] box
@@ -108,6 +110,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
   // shared-memory bandwidth (both operands streamed from shared memory for every step).
   constexpr uint32_t A_BASE = BUF_BASE + 256;               // TMEM column of the resident copies
   constexpr bool A_IN_TMEM = A_BASE + Sm::N_A * (D / 2) <= 512;
+  // FUSED: where dQ^T (64 fp32 columns) lives. D = 128 has no free columns, so it takes the step's
+  // T2 columns once dP^T has been consumed; D = 64 has 64 columns left after the resident copies.
+  constexpr bool DQ_ALIASED = D == 128;
+  constexpr uint32_t DQ_COL_FIXED = A_BASE + Sm::N_A * (D / 2);
+  static_assert(!FUSED || DQ_ALIASED || DQ_COL_FIXED + 64 <= 512, "no TMEM columns for dQ^T");
+  auto dq_col = [](int buf) -> uint32_t { return DQ_ALIASED ? BUF_BASE + buf * 128 + 64 : DQ_COL_FIXED; };
+  // (single fixed buffer: one barrier pair, phase = step parity; aliased: one pair per T buffer)
+  auto dq_slot = [](int i) -> int { return DQ_ALIASED ? (i & 1) : 0; };
+  auto dq_phase = [](int i) -> uint32_t { return DQ_ALIASED ? ((i >> 1) & 1) : (i & 1); };
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -304,7 +315,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           mma_ts_w(d, a + (s >> 1) * 32 + (s & 1) * 8, db + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_ACC,
                    (accumulate || s > 0) ? 1u : 0u);
       };
-      // FUSED: dQ^T (128 feature rows x 64 queries) = K^T dS^T into the T2 columns of buffer `buf`.
+      // FUSED: dQ^T (feature rows x 64 queries) = K^T dS^T. The product always has M = 128: at
+      // D = 64 the MN-major descriptor runs on from the K tile into the V tile behind it, so lanes
+      // 64..127 receive V^T dS^T, which nobody reads.
       auto issue_dq = [&](int buf) {
         constexpr uint32_t IDESC_DQ = make_idesc(BF16, 128, STEP, true, true);
         constexpr uint64_t DS_DESC = make_smem_desc_hi(Sm::DS_TILE_BYTES, 1024, SWZ_128B);
@@ -312,7 +325,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         const uint64_t db = smem_desc(DS_DESC, smem_u32(sDS));
 #pragma unroll
         for (int s = 0; s < 128 / 16; ++s)
-          mma_ss_w(tmem_base + BUF_BASE + buf * 128 + 64, da + ((s * 16 * Cfg::ROW_BYTES) >> 4),
+          mma_ss_w(tmem_base + dq_col(buf), da + ((s * 16 * Cfg::ROW_BYTES) >> 4),
                    db + ((s * 16 * 128) >> 4), IDESC_DQ, s > 0 ? 1u : 0u);
       };
       bool ok = true;
@@ -333,11 +346,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           B200ATTN_STAMP(1, 4 * i + 0);
           const bool w = wait(&b_full[st_next], ((i + 1) / STAGES) & 1);
           if (!__all_sync(0xffffffffu, w)) { fail(ST_WAIT_TMA); ok = false; break; }
-          if constexpr (FUSED) {
+          if constexpr (FUSED && DQ_ALIASED) {
             // the T2 columns of the other buffer still hold dQ^T of step i - 1 until it is read back
             if (i >= 1) {
               B200ATTN_STAMP(3, 2 * i + 0);
-              const bool w2 = wait(&dq_drained[buf ^ 1], ((i - 1) >> 1) & 1);
+              const bool w2 = wait(&dq_drained[dq_slot(i - 1)], dq_phase(i - 1));
               B200ATTN_STAMP(3, 2 * i + 1);
               if (!__all_sync(0xffffffffu, w2)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
             }
@@ -356,10 +369,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         B200ATTN_STAMP(1, 4 * i + 3);
         if constexpr (MODE == MODE_KV) {
           if constexpr (FUSED) {
-            // first, so that its read-back overlaps the two accumulating products and the T2
-            // columns are free again when the next T products are issued
+            if constexpr (!DQ_ALIASED) {
+              // one fixed dQ^T buffer: the previous step's must have been read back
+              if (i >= 1) {
+                const bool w2 = wait(&dq_drained[0], dq_phase(i - 1));
+                if (!__all_sync(0xffffffffu, w2)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
+                tc_fence_after();
+              }
+            }
+            // first, so that its read-back overlaps the two accumulating products and (aliased)
+            // the T2 columns are free again when the next T products are issued
             issue_dq(buf);
-            tc_commit_w(&dq_ready[buf]);
+            tc_commit_w(&dq_ready[dq_slot(i)]);
           }
           issue_acc(1, buf, 0, st, 1, i > 0);  // dV += P^T  dO
           issue_acc(0, buf, 1, st, 0, i > 0);  // dK += dS^T Q
@@ -382,17 +403,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         const int col = col_lo + (i - hh * steps_per_head) * STEP;
         if (warp == 10) B200ATTN_STAMP(2, 4 * i + 0);
         {
-          const bool w = wait(&dq_ready[buf], (i >> 1) & 1);
+          const bool w = wait(&dq_ready[dq_slot(i)], dq_phase(i));
           if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); break; }
         }
         if (warp == 10) B200ATTN_STAMP(2, 4 * i + 1);
         tc_fence_after();
         uint32_t v[STEP];
-        tmem_ld32(tmem_base + lane_base + BUF_BASE + buf * 128 + 64, v);
-        tmem_ld32(tmem_base + lane_base + BUF_BASE + buf * 128 + 96, v + 32);
+        tmem_ld32(tmem_base + lane_base + dq_col(buf), v);
+        tmem_ld32(tmem_base + lane_base + dq_col(buf) + 32, v + 32);
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(&dq_drained[buf]);
+        mbar_arrive(&dq_drained[dq_slot(i)]);
         if (warp == 10) B200ATTN_STAMP(2, 4 * i + 2);
         // Out through shared memory, 32 queries at a time: the tile is laid out like the
         // accumulator rows ([query][feature], contiguous in global memory) and one bulk
@@ -408,7 +429,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           asm volatile("bar.sync 2, 128;" ::: "memory");
           float* stage = stage0 + half * (Sm::DQ_STAGE_BYTES / 4);
 #pragma unroll
-          for (int c = 0; c < 32; ++c) stage[c * D + d] = __uint_as_float(v[half * 32 + c]);
+          for (int c = 0; c < 32; ++c)
+            if (d < D) stage[c * D + d] = __uint_as_float(v[half * 32 + c]);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           asm volatile("bar.sync 2, 128;" ::: "memory");
           if (threadIdx.x == 320 && rows_out > 0) {
@@ -547,7 +569,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           // bytes, 16-byte chunks permuted by the 128-byte swizzle.
           // (one tile: the product that read the previous step's copy must have completed)
           if (i >= 1) {
-            const bool w = wait(&dq_ready[buf ^ 1], ((i - 1) >> 1) & 1);
+            const bool w = wait(&dq_ready[dq_slot(i - 1)], dq_phase(i - 1));
             if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
           }
           uint8_t* ds_row = sDS + row_local * 128;

@@ -10,7 +10,7 @@ struct BwdLaunch {
   BwdArgs args;
   dim3 grid;
   bool bf16, dropout;
-  bool fused = false;  // MODE_KV, D = 128: dQ produced in the same pass (args.dq_acc)
+  bool fused = false;  // MODE_KV, D = 128 or 64: dQ produced in the same pass (args.dq_acc)
   int mode;
   cudaStream_t stream;
 };
@@ -37,7 +37,7 @@ int launch_bwd_d(const BwdLaunch& L) {
     return L.bf16 ? launch_bwd_variant<D, true, false, MODE_TOTAL>(L)
                   : launch_bwd_variant<D, false, false, MODE_TOTAL>(L);
   }
-  if constexpr (D == 128) {
+  if constexpr (D == 128 || D == 64) {
     if (L.mode == MODE_KV && L.fused) {
       if (L.bf16) return L.dropout ? launch_bwd_variant<D, true, true, MODE_KV, true>(L) : launch_bwd_variant<D, true, false, MODE_KV, true>(L);
       return L.dropout ? launch_bwd_variant<D, false, true, MODE_KV, true>(L) : launch_bwd_variant<D, false, false, MODE_KV, true>(L);

@@ -260,7 +260,7 @@ class FlashAttentionFunction(torch.autograd.Function):
                 B, H, Hk, M, N, D, _lib.dtype_code(q.dtype), _lib.dtype_code(o.dtype),
                 int(ctx.causal), float(ctx.sm_scale), float(ctx.dropout_p),
                 as_u64(ctx.seed), as_u64(ctx.offset), status.data_ptr())
-            # At D = 128 the library produces dQ inside the dK/dV pass, summing the key blocks'
+            # At D = 128 and 64 the library produces dQ inside the dK/dV pass, summing the key blocks'
             # contributions by fp32 reductions in global memory: faster, but the summation order (and
             # so the last bit of dQ) can differ between runs. torch.use_deterministic_algorithms(True)
             # selects the two separate kernels, whose results are reproducible bit for bit.

@@ -124,7 +124,7 @@ int b200attn_bwd(const b200attn_bwd_params* p, void* stream);
 
 /* The same backward restricted to some of its stages, so a profiler or benchmark can time the
  * kernels one by one. PREP = delta + statistics preprocess, KV = the dK/dV kernel, Q = the dQ
- * kernel; KV and Q need the scratch PREP wrote. At D = 128 the KV stage is a fused pass that also
+ * kernel; KV and Q need the scratch PREP wrote. At D = 128 and 64 the KV stage is a fused pass that also
  * accumulates dQ in fp32 (in the workspace, by global reductions, so dQ is reproducible only up to
  * fp32 summation order) and the Q stage is the conversion of that accumulator; adding UNFUSED
  * selects the two separate kernels instead. No counterpart in the reference. */

@@ -120,9 +120,9 @@ def test_attention_bwd(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
 
 
 @pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,scale",
-                         [p for p in _params([s for s in BWD_SHAPES if s[5] == 128])])
+                         [p for p in _params([s for s in BWD_SHAPES if s[5] in (64, 128)])])
 def test_attention_bwd_deterministic_mode(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
-    """Under torch.use_deterministic_algorithms(True) head dimension 128 uses the two separate
+    """Under torch.use_deterministic_algorithms(True) head dimensions 128 and 64 use the two separate
     backward kernels instead of the fused pass with global reductions: same parity rule, and two runs
     agree bit for bit."""
     q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, layout, scale, seed=10086, requires_grad=True)

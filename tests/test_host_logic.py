@@ -64,3 +64,26 @@ def test_contract_violations_raise_like_the_reference():
         flash_attention(q, k, k)
     with pytest.raises(RuntimeError, match="CUDA"):
         flash_attention(q, q, q)  # CPU tensors: there is no CPU path
+
+
+def test_bench_flash_record_rows_have_the_reference_recorder_keys(tmp_path, monkeypatch):
+    """The sweep's log line carries the row keys of the reference's recorder
+    (benchmark/recording.py:36-54) and its FLOP formula (benchmark/flash_benchmark.py:120-128)."""
+    import json
+
+    from flagattention_b200 import bench_flash
+
+    assert bench_flash.ROW_KEYS == (
+        "case_id", "candidate_source", "legacy_shape", "shape_detail", "latency_base", "latency", "gbps_base",
+        "gbps", "speedup", "accuracy", "tflops", "utilization", "compared_speedup", "base_miss_reason", "error_msg")
+    # batch 32768 // 4096 = 8, heads 2048 // 128 = 16
+    assert bench_flash.flops(4096, 128, False, "fwd") == 4.0 * 8 * 16 * 4096 * 4096 * 128
+    assert bench_flash.flops(4096, 128, True, "bwd") == 4.0 * 8 * 16 * 4096 * 4096 * 128 * 2.5 * 0.5
+    log = tmp_path / "sub" / "bench.log"
+    monkeypatch.setenv(bench_flash.LOG_PATH_ENV, str(log))
+    bench_flash.emit({"level": "comprehensive", "op_name": "flash_attention", "dtype": "torch.bfloat16",
+                      "mode": "kernel", "result": [dict.fromkeys(bench_flash.ROW_KEYS)]})
+    line = log.read_text().strip()
+    assert line.startswith("[INFO] ")
+    detail = json.loads(line[len("[INFO] "):])
+    assert detail["op_name"] == "flash_attention" and set(detail["result"][0]) == set(bench_flash.ROW_KEYS)
