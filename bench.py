@@ -61,7 +61,8 @@ NCU_TRAFFIC_BYTES = {
     # (dram read + write) MB measured at batch 2, scaled x2 to the batch-4 workload (traffic is
     # proportional to batch); the capture is summarised under profiles/
     "c2_gqa_prefill_train": {"bwd_kernel<kv>": 2 * (220.867072e6 + 22.053632e6),
-                             "fwd_kernel": 2 * (101.170944e6 + 31.920384e6)},  # fused pass: see below
+                             "bwd_kernel<kv+dq>": 2 * (468.678144e6 + 205.996544e6),
+                             "fwd_kernel": 2 * (101.170944e6 + 31.920384e6)},
 }
 
 
