@@ -1,7 +1,8 @@
 """B200-native drop-in for ``flag_attn.flash_attention``."""
 from .flash import (FlashAttentionFunction, check_device_status, flash_attention,  # noqa: F401
                     flash_attention_split_kv)
+from .paged import paged_attention  # noqa: F401
 
-__all__ = ["flash_attention", "flash_attention_split_kv", "FlashAttentionFunction",
+__all__ = ["flash_attention", "flash_attention_split_kv", "paged_attention", "FlashAttentionFunction",
            "check_device_status"]
 __version__ = "0.1.0"

@@ -71,6 +71,17 @@ class SplitKVParams(Structure):
     ]
 
 
+class PagedParams(Structure):
+    _fields_ = [
+        ("q", Tensor4), ("key_cache", Tensor4), ("value_cache", Tensor4), ("o", Tensor4),
+        ("block_table", c_void_p), ("block_table_stride", c_int64), ("context_lens", c_void_p),
+        ("lse", c_void_p), ("part_o", c_void_p), ("part_lse", c_void_p),
+        ("num_seqs", c_int32), ("Hq", c_int32), ("Hkv", c_int32), ("D", c_int32), ("block_size", c_int32),
+        ("num_blocks", c_int32), ("max_context_len", c_int32), ("num_splits", c_int32),
+        ("dtype", c_int32), ("sm_scale", c_float), ("status", c_void_p),
+    ]
+
+
 class SelftestParams(Structure):
     _fields_ = [
         ("a", c_void_p), ("b", c_void_p), ("d", c_void_p),
@@ -101,6 +112,7 @@ SYMBOLS = {
                                         c_uint64, c_void_p]),
     "b200attn_fwd_splitkv": (c_int32, [POINTER(SplitKVParams), c_void_p]),
     "b200attn_splitkv_num_splits": (c_int32, [c_int32] * 7),
+    "b200attn_paged_attention": (c_int32, [POINTER(PagedParams), c_void_p]),
     "b200attn_merge_partial": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200attn_abi_version": (c_int32, []),

@@ -62,7 +62,9 @@ decode_partial_kernel(const DecodeArgs a) {
   const int hk = bhk % a.Hkv;
   const int b = bhk / a.Hkv;
   const int rows = a.groups * a.M;  // <= R
-  const int P_SEQ = a.N - a.M;
+  const bool paged = a.block_table != nullptr;
+  const int N = paged ? a.context_lens[b] : a.N;
+  const int P_SEQ = N - a.M;
 
   // Query rows (head-major within the KV head's group) and their visible key limits.
   float q[R][8];
@@ -75,7 +77,7 @@ decode_partial_kernel(const DecodeArgs a) {
       const uint16_t* qp = a.q + b * a.q_sb + static_cast<int64_t>(hk * a.groups + g) * a.q_sh +
                            static_cast<int64_t>(m) * a.q_sm + sub * 8;
       unpack8<BF16>(*reinterpret_cast<const uint4*>(qp), q[r]);
-      lim[r] = a.causal ? min(a.N, max(0, P_SEQ + m + 1)) : a.N;
+      lim[r] = a.causal ? min(N, max(0, P_SEQ + m + 1)) : N;
     } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) q[r][i] = 0.f;
@@ -86,8 +88,22 @@ decode_partial_kernel(const DecodeArgs a) {
 
   const int n_lo = split * a.keys_per_split;
   const int n_hi = min(lim_max, n_lo + a.keys_per_split);
-  const uint16_t* kbase = a.k + b * a.k_sb + static_cast<int64_t>(hk) * a.k_sh + sub * 8;
-  const uint16_t* vbase = a.v + b * a.v_sb + static_cast<int64_t>(hk) * a.v_sh + sub * 8;
+  const uint16_t* kbase = a.k + (paged ? 0 : b * a.k_sb) + static_cast<int64_t>(hk) * a.k_sh + sub * 8;
+  const uint16_t* vbase = a.v + (paged ? 0 : b * a.v_sb) + static_cast<int64_t>(hk) * a.v_sh + sub * 8;
+  const int32_t* table = paged ? a.block_table + b * a.bt_stride : nullptr;
+  const int block_mask = (1 << a.block_shift) - 1;
+  // Element offsets of key n's row in K and V.
+  auto row_offsets = [&](int n, int64_t& ko, int64_t& vo) {
+    if (paged) {
+      const int64_t blk = __ldg(table + (n >> a.block_shift));
+      const int64_t r = n & block_mask;
+      ko = blk * a.k_sb + r * a.k_sn;
+      vo = blk * a.v_sb + r * a.v_sn;
+    } else {
+      ko = static_cast<int64_t>(n) * a.k_sn;
+      vo = static_cast<int64_t>(n) * a.v_sn;
+    }
+  };
 
   float m_run[R], l_run[R], acc[R][8];
 #pragma unroll
@@ -111,8 +127,10 @@ decode_partial_kernel(const DecodeArgs a) {
     for (int u = 0; u < DEC_UNROLL; ++u) {
       const int n = first_key + u * STEP;
       if (n < n_hi) {
-        kr[u] = ldg_stream(kbase + static_cast<int64_t>(n) * a.k_sn);
-        vr[u] = ldg_stream(vbase + static_cast<int64_t>(n) * a.v_sn);
+        int64_t ko, vo;
+        row_offsets(n, ko, vo);
+        kr[u] = ldg_stream(kbase + ko);
+        vr[u] = ldg_stream(vbase + vo);
       } else {
         kr[u] = make_uint4(0, 0, 0, 0);
         vr[u] = make_uint4(0, 0, 0, 0);

@@ -30,6 +30,13 @@ struct DecodeArgs {
   int num_splits, keys_per_split;
   int causal;
   float qk_scale;            // sm_scale * log2(e)
+  // Paged K/V (block_table != nullptr): k and v point at caches [num_blocks, Hkv, block, D]; key n of
+  // sequence b lives in block block_table[b * bt_stride + (n >> block_shift)] at row n & (block - 1);
+  // k_sb / v_sb are then the block strides and N is read per sequence from context_lens.
+  const int32_t* block_table;
+  int64_t bt_stride;
+  const int32_t* context_lens;
+  int block_shift;
 };
 
 int launch_decode_partial(const DecodeArgs& a, int D, bool bf16, cudaStream_t stream);

@@ -63,7 +63,7 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
     return B200ATTN_EINVAL;
   }
 
-  FwdLaunch L;
+  FwdLaunch L{};  // zero: every optional mode (packing, paging) is off unless set below
   int rc;
   switch (p->D) {
     case 16: rc = make_fwd_tmaps<16>(p, L); break;
@@ -166,8 +166,18 @@ static int launch_splitkv_combine(const b200attn_splitkv_params* p, bool bf16, u
 
 }  // namespace b200attn
 
-extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stream_) {
-  using namespace b200attn;
+namespace b200attn {
+
+// Paged K/V description for the split-KV pass (nullptr = dense k, v of shape [B, Hkv, N, D]). With
+// it, p->k and p->v are caches [num_blocks, Hkv, block, D] and p->N is the largest context length.
+struct PagedKV {
+  const int32_t* block_table;
+  int64_t bt_stride;
+  const int32_t* context_lens;
+  int block, block_shift, num_blocks;
+};
+
+static int run_splitkv(const b200attn_splitkv_params* p, const PagedKV* paged, void* stream_) {
   if (p == nullptr) {
     set_error("fwd_splitkv: null params");
     return B200ATTN_EINVAL;
@@ -213,7 +223,8 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
     if (rc == B200ATTN_OK) rc = check_tma_operand(p->v, 2, "v");
     if (rc != B200ATTN_OK) return rc;
     const b200attn_tensor* ops[3] = {&p->q, &p->k, &p->v};
-    const int64_t ext[3][3] = {{p->B, p->Hq, p->M}, {p->B, p->Hkv, p->N}, {p->B, p->Hkv, p->N}};
+    const int64_t kv0 = paged ? paged->num_blocks : p->B, kv2 = paged ? paged->block : p->N;
+    const int64_t ext[3][3] = {{p->B, p->Hq, p->M}, {kv0, p->Hkv, kv2}, {kv0, p->Hkv, kv2}};
     for (int t = 0; t < 3; ++t) {
       for (int i = 0; i < 3; ++i) {
         if (ext[t][i] > 1 && ops[t]->stride[i] % 8 != 0) {
@@ -241,6 +252,12 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
     d.keys_per_split = cdiv(n_blocks, S) * 128;
     d.causal = p->causal ? 1 : 0;
     d.qk_scale = p->sm_scale * 1.4426950408889634f;
+    if (paged) {
+      d.block_table = paged->block_table;
+      d.bt_stride = paged->bt_stride;
+      d.context_lens = paged->context_lens;
+      d.block_shift = paged->block_shift;
+    }
     if (p->num_splits == 1) {
       d.final_o = static_cast<uint16_t*>(p->o.ptr);
       d.final_lse = p->lse;
@@ -256,7 +273,7 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
   b200attn_fwd_params f{};
   f.q = p->q; f.k = p->k; f.v = p->v;
   f.B = p->B; f.Hq = p->Hq; f.Hkv = p->Hkv; f.M = p->M; f.N = p->N; f.D = p->D;
-  FwdLaunch L;
+  FwdLaunch L{};  // zero: every optional mode (packing, paging) is off unless set below
   int rc;
   switch (p->D) {
     case 16: rc = make_fwd_tmaps<16>(&f, L); break;
@@ -265,6 +282,21 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
     default: rc = make_fwd_tmaps<128>(&f, L); break;
   }
   if (rc) return rc;
+  if (paged) {
+    if (paged->block < 8) {
+      set_error("paged attention: cache blocks of fewer than 8 keys need at most 2 query heads per KV head");
+      return B200ATTN_EUNSUPPORTED;
+    }
+    const int chunk = p->D >= 64 ? 64 : p->D;
+    const int swz = p->D >= 64 ? 3 : (p->D == 32 ? 2 : 1);
+    const int box_rows = paged->block < 128 ? paged->block : 128;
+    rc = encode_tmap_4d(&L.tmK, p->k, 2, paged->num_blocks, p->Hkv, paged->block, p->D, chunk, box_rows, swz,
+                        "key_cache");
+    if (rc) return rc;
+    rc = encode_tmap_4d(&L.tmV, p->v, 2, paged->num_blocks, p->Hkv, paged->block, p->D, chunk, box_rows, swz,
+                        "value_cache");
+    if (rc) return rc;
+  }
   // Decode-style shapes with grouped heads: all query heads of a KV head share one 128-row tile, so
   // every K/V tile is fetched once per KV head instead of once per query head.
   const int groups = p->Hq / p->Hkv;
@@ -293,6 +325,12 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
   a.tiles_per_split = cdiv(n_blocks, cta_splits < n_blocks ? cta_splits : n_blocks);
   a.pack_heads = packed ? groups : 0;
   a.dual_stream = dual ? 1 : 0;
+  if (paged) {
+    a.block_table = paged->block_table;
+    a.bt_stride = paged->bt_stride;
+    a.context_lens = paged->context_lens;
+    a.block_shift = paged->block_shift;
+  }
   a.ring_stages = p->D == 128 ? FwdSmem<128>::DUAL_STAGES
                   : p->D == 64 ? FwdSmem<64>::DUAL_STAGES
                   : p->D == 32 ? FwdSmem<32>::DUAL_STAGES : FwdSmem<16>::DUAL_STAGES;
@@ -318,6 +356,46 @@ extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stre
   }
   if (rc) return rc;
   return launch_splitkv_combine(p, L.bf16, static_cast<unsigned>(rows), L.stream);
+}
+
+}  // namespace b200attn
+
+extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stream) {
+  return b200attn::run_splitkv(p, nullptr, stream);
+}
+
+extern "C" int b200attn_paged_attention(const b200attn_paged_params* p, void* stream) {
+  using namespace b200attn;
+  if (p == nullptr) {
+    set_error("paged_attention: null params");
+    return B200ATTN_EINVAL;
+  }
+  if (p->num_seqs <= 0 || p->num_blocks <= 0 || p->block_size <= 0 || p->max_context_len <= 0 ||
+      p->block_table == nullptr || p->context_lens == nullptr) {
+    set_error("paged_attention: bad shape or null table");
+    return B200ATTN_EINVAL;
+  }
+  if ((p->block_size & (p->block_size - 1)) != 0) {
+    set_error("paged_attention: block size %d is not a power of two", p->block_size);
+    return B200ATTN_EUNSUPPORTED;
+  }
+  PagedKV pk{};
+  pk.block_table = p->block_table;
+  pk.bt_stride = p->block_table_stride;
+  pk.context_lens = p->context_lens;
+  pk.block = p->block_size;
+  pk.num_blocks = p->num_blocks;
+  while ((1 << pk.block_shift) < p->block_size) ++pk.block_shift;
+  b200attn_splitkv_params sp{};
+  sp.q = p->q; sp.k = p->key_cache; sp.v = p->value_cache; sp.o = p->o;
+  sp.lse = p->lse; sp.part_o = p->part_o; sp.part_lse = p->part_lse;
+  sp.B = p->num_seqs; sp.Hq = p->Hq; sp.Hkv = p->Hkv; sp.M = 1; sp.N = p->max_context_len; sp.D = p->D;
+  sp.num_splits = p->num_splits;
+  sp.dtype = p->dtype;
+  sp.causal = 0;
+  sp.sm_scale = p->sm_scale;
+  sp.status = p->status;
+  return run_splitkv(&sp, &pk, stream);
 }
 
 namespace b200attn {

@@ -54,6 +54,14 @@ struct FwdArgs {
                                     // tiles take alternate K/V tiles of the CTA's key range, as two
                                     // independent softmax chains; tile t writes partial 2 * split + t
   int ring_stages;                  // dual_stream: K/V ring depth (one shared Q tile leaves room for more)
+  // Paged K/V (block_table != nullptr): the K and V tensor maps describe caches [num_blocks, Hkv,
+  // block, D] with boxes of min(block, 128) rows; key n of sequence b lives in block
+  // block_table[b * bt_stride + (n >> block_shift)] at row n & (block - 1), and the sequence's
+  // key count comes from context_lens[b] instead of N.
+  const int32_t* block_table;
+  int64_t bt_stride;
+  const int32_t* context_lens;
+  int block_shift;
   int B, Hq, Hkv, M, N, groups;
   int causal, o_fp32;
   float sm_scale, qk_scale;
@@ -85,11 +93,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
 static constexpr float RESCALE_THRESHOLD = 8.0f;
 
 // Which of every 8 consecutive column pairs compute their exponential with the polynomial on the
-// FMA pipe instead of ex2.approx on the special-function unit (bit k = pair k).
-#ifndef B200ATTN_FWD_POLY_MASK
-#define B200ATTN_FWD_POLY_MASK 0x00u
+// FMA pipe instead of ex2.approx on the special-function unit (bit k = pair k). The smaller the head
+// dimension, the fewer tensor-core cycles stand against the 16-per-clock special-function unit, so
+// the larger the share that pays.
+#ifndef B200ATTN_FWD_POLY_MASK_D128
+#define B200ATTN_FWD_POLY_MASK_D128 0x11u
 #endif
-static constexpr uint32_t POLY_MASK = B200ATTN_FWD_POLY_MASK;
+#ifndef B200ATTN_FWD_POLY_MASK_SMALL_D
+#define B200ATTN_FWD_POLY_MASK_SMALL_D 0x11u
+#endif
+template <int D>
+struct PolyMask {
+  static constexpr uint32_t value = D >= 128 ? B200ATTN_FWD_POLY_MASK_D128 : B200ATTN_FWD_POLY_MASK_SMALL_D;
+};
 
 template <int D, bool BF16, bool DROPOUT>
 __global__ void __launch_bounds__(384, 1)
@@ -134,19 +150,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const int hk = packed ? bc.bh % grid_heads : (bc.bh % grid_heads) / args.groups;
   const int h = packed ? hk * args.groups : bc.bh % grid_heads;   // first (or only) query head
   const int m0 = m_blk * 2 * BLOCK;
-  const int P_SEQ = args.N - args.M;
+  const bool paged = args.block_table != nullptr;
+  const int N_ctx = paged ? args.context_lens[b] : args.N;
+  const int P_SEQ = N_ctx - args.M;
 
   // Number of K/V tiles each query tile visits.
   int n_tiles[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int mt = m0 + t * BLOCK;
-    int hi = args.N;
-    if (args.causal) hi = min(args.N, max(0, P_SEQ + mt + BLOCK));
+    int hi = N_ctx;
+    if (args.causal) hi = min(N_ctx, max(0, P_SEQ + mt + BLOCK));
     int n_full = mt < args.M ? cdiv(hi, BLOCK) : 0;
     if (packed) {
       // one tile holds every row of every head of the group: rows m = 0..M-1
-      const int hi_p = args.causal ? min(args.N, max(0, P_SEQ + args.M)) : args.N;
+      const int hi_p = args.causal ? min(N_ctx, max(0, P_SEQ + args.M)) : N_ctx;
       n_full = t == 0 ? cdiv(hi_p, BLOCK) : 0;
     }
     n_tiles[t] = max(0, min(n_full, j0 + args.tiles_per_split) - j0);
@@ -226,15 +244,30 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       for (int j = 0; j < n_max; ++j, ++st) {
         if (st == stages) { st = 0; par ^= 1; }
         if (!wait(&k_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
-        mbar_expect_tx(&k_full[st], Cfg::TILE_BYTES);
-        for (int c = 0; c < Cfg::NCHUNK; ++c)
-          tma_load_4d(sK + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmK, &k_full[st],
-                      c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
+        // One tile = 128 consecutive keys: a single box of the dense tensor, or (paged) as many
+        // boxes as cache blocks the tile spans. Boxes past the sequence's last block re-read that
+        // block, so the tile holds finite numbers everywhere (those keys are masked).
+        auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar) {
+          mbar_expect_tx(bar, Cfg::TILE_BYTES);
+          if (!paged) {
+            for (int c = 0; c < Cfg::NCHUNK; ++c)
+              tma_load_4d(dst + c * Cfg::CHUNK_BYTES, tm, bar, c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
+          } else {
+            const int block = 1 << args.block_shift;
+            const int box_rows = min(block, BLOCK);
+            const int last_blk = (N_ctx - 1) >> args.block_shift;
+            for (int r = 0; r < BLOCK; r += box_rows) {
+              const int n_start = (j0 + j) * BLOCK + r;
+              const int blk = args.block_table[b * args.bt_stride + min(n_start >> args.block_shift, last_blk)];
+              for (int c = 0; c < Cfg::NCHUNK; ++c)
+                tma_load_4d(dst + c * Cfg::CHUNK_BYTES + r * Cfg::ROW_BYTES, tm, bar, c * Cfg::CHUNK,
+                            n_start & (block - 1), hk, blk);
+            }
+          }
+        };
+        load_tile(sK + st * Cfg::TILE_BYTES, &tmK, &k_full[st]);
         if (!wait(&v_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
-        mbar_expect_tx(&v_full[st], Cfg::TILE_BYTES);
-        for (int c = 0; c < Cfg::NCHUNK; ++c)
-          tma_load_4d(sV + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmV, &v_full[st],
-                      c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
+        load_tile(sV + st * Cfg::TILE_BYTES, &tmV, &v_full[st]);
       }
     }
     __syncwarp();
@@ -269,6 +302,24 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                    dv + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_PV, (acc || s > 0) ? 1u : 0u);
         }
       };
+      // Paged caches only: the last block of a sequence holds rows past its context length whose
+      // contents are arbitrary. Their probabilities are exactly zero, but 0 x NaN is NaN in the
+      // product, so those V rows are cleared in shared memory before P V reads them.
+      auto clear_stale_v_rows = [&](int st, int j) {
+        if (!paged) return;
+        const int first_bad = N_ctx - (j0 + j) * BLOCK;
+        if (first_bad >= BLOCK) return;
+        uint8_t* tile = sV + st * Cfg::TILE_BYTES;
+        for (int r = max(first_bad, 0) + lane; r < BLOCK; r += 32) {
+          for (int c = 0; c < Cfg::NCHUNK; ++c) {
+            uint4* row = reinterpret_cast<uint4*>(tile + c * Cfg::CHUNK_BYTES + r * Cfg::ROW_BYTES);
+#pragma unroll
+            for (int k = 0; k < Cfg::ROW_BYTES / 16; ++k) row[k] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+      };
       auto wait_all = [&](uint64_t* bar, uint32_t parity, int32_t code) -> bool {
         const bool w = wait(bar, parity);
         if (__all_sync(0xffffffffu, w)) return true;
@@ -293,6 +344,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           const int t = j & 1, jj = j >> 1;
           const bool more = j + 2 < n_max;
           if (!wait_all(&v_full[st], ph, ST_WAIT_TMA)) break;
+          clear_stale_v_rows(st, j);
           if (more) {
             if (!wait_all(&k_full[st2], ph2, ST_WAIT_TMA)) break;
           }
@@ -329,6 +381,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const int st = j % STAGES;
         const int st_next = (j + 1) % STAGES;
         if (!wait_all(&v_full[st], (j / STAGES) & 1, ST_WAIT_TMA)) break;
+        clear_stale_v_rows(st, j);
         if (j + 1 < n_max) {
           if (!wait_all(&k_full[st_next], ((j + 1) / STAGES) & 1, ST_WAIT_TMA)) break;
         }
@@ -369,15 +422,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const int nt = n_tiles[t];
     const float qk_scale = args.qk_scale;
     // Keys n < lim are visible to this row.
-    const int lim = args.causal ? min(args.N, P_SEQ + m_glob + 1) : args.N;
+    const int lim = args.causal ? min(N_ctx, P_SEQ + m_glob + 1) : N_ctx;
     // Tiles j with (j+1)*128 <= full_upto need no masking for any row of the tile.
-    const int full_upto = args.causal ? min(args.N, P_SEQ + (packed ? 0 : m0 + t * BLOCK) + 1) : args.N;
+    const int full_upto = args.causal ? min(N_ctx, P_SEQ + (packed ? 0 : m0 + t * BLOCK) + 1) : N_ctx;
     const int split_out = dual ? 2 * split + t : split;
     uint64_t ctr_row = 0;
     if constexpr (DROPOUT) {
       ctr_row = args.drop.offset +
                 ((static_cast<uint64_t>(b) * args.Hq + h_row) * args.M + static_cast<uint64_t>(m_glob)) *
-                    static_cast<uint64_t>(args.N);
+                    static_cast<uint64_t>(N_ctx);
     }
 
     float m_run = -INFINITY;
@@ -466,15 +519,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
         for (int i = half * 64; i < half * 64 + 64; i += 4) {
           float p0, p1, p2, p3;
-          // A fixed subset of the column pairs takes the polynomial route (see POLY_MASK).
-          if ((POLY_MASK >> ((i >> 1) & 7)) & 1u) {
+          // A fixed subset of the column pairs takes the polynomial route (see PolyMask).
+          if ((PolyMask<D>::value >> ((i >> 1) & 7)) & 1u) {
             exp2_poly_pair(f2_fma(f2_pack(__uint_as_float(s[i + 0]), __uint_as_float(s[i + 1])), scale2, neg_ms2),
                            p0, p1);
           } else {
             p0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), qk_scale, neg_ms));
             p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_ms));
           }
-          if ((POLY_MASK >> (((i >> 1) + 1) & 7)) & 1u) {
+          if ((PolyMask<D>::value >> (((i >> 1) + 1) & 7)) & 1u) {
             exp2_poly_pair(f2_fma(f2_pack(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), scale2, neg_ms2),
                            p2, p3);
           } else {

@@ -176,6 +176,37 @@ int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stream);
 int b200attn_splitkv_num_splits(int32_t B, int32_t Hq, int32_t Hkv, int32_t M, int32_t N, int32_t D,
                                 int32_t num_sms);
 
+/* Decode attention over a paged K/V cache: replaces `_paged_attn_kernel` + `_paged_attn_v2_reduce_kernel`
+ * as launched by `paged.attention` (paged.py:20-170). One query row per sequence.
+ *   q, o          [num_seqs, Hq, D] described as 4-D tensors [num_seqs, Hq, 1, D] (stride[2] unused)
+ *   key_cache,
+ *   value_cache   [num_blocks, Hkv, block_size, D]; key n of sequence s is row n % block_size of block
+ *                 block_table[s * block_table_stride + n / block_size]
+ *   context_lens  [num_seqs] int32, keys per sequence (<= max_context_len)
+ *   lse           [num_seqs, Hq] fp32 out (log-normaliser; the reference does not return it)
+ *   part_o/_lse   fp32 scratch [num_seqs, Hq, num_splits, D] / [num_seqs, Hq, num_splits], part_o
+ *                 16-byte aligned; any num_splits >= 1 gives the same result up to fp32 rounding
+ *                 (b200attn_splitkv_num_splits(num_seqs, Hq, Hkv, 1, max_context_len, D, 0) is the
+ *                 tuned choice; the reference's own `num_splits` argument only tunes its kernels).
+ * block_size must be a power of two (the reference accepts any size; its tests use 16, 128, 256),
+ * and at least 8 when more than 2 query heads share a KV head. D in {16, 32, 64, 128} (the reference
+ * also lists 256 and 512). Table entries beyond a sequence's last block are never read. */
+typedef struct {
+  b200attn_tensor q, key_cache, value_cache, o;
+  const int32_t* block_table;
+  int64_t block_table_stride;
+  const int32_t* context_lens;
+  float* lse;
+  float* part_o;
+  float* part_lse;
+  int32_t num_seqs, Hq, Hkv, D, block_size, num_blocks, max_context_len, num_splits;
+  int32_t dtype;
+  float sm_scale;
+  int32_t* status;
+} b200attn_paged_params;
+
+int b200attn_paged_attention(const b200attn_paged_params* p, void* stream);
+
 /* Merge of two partial attention results over disjoint key sets, in place on the accumulator:
  * lse = log(exp(lse_acc) + exp(lse_part)), o_acc = o_acc*exp(lse_acc-lse) + o_part*exp(lse_part-lse).
  * Both sides are contiguous fp32 arrays [heads, rows_per_head, D] (o) and [heads, rows_per_head]

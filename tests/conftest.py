@@ -58,3 +58,19 @@ ATTENTION_GOLDENS = ["attention_c1_plumbing", "attention_gqa_causal_bf16", "atte
                      "attention_larger_m_causal", "attention_dropout_fp16", "attention_dropout_bf16_gqa"]
 TRITON_GOLDENS = ["triton_interp_causal0_p0", "triton_interp_causal0_p3", "triton_interp_causal1_p0",
                   "triton_interp_causal1_p3"]
+
+
+PAGED_GOLDENS = ["paged_mha_fp16", "paged_gqa8_fp16", "paged_gqa4_bf16"]
+
+
+def load_paged_golden(name: str) -> dict:
+    """A paged-attention fixture of tests/golden/make_golden.py: q, key_cache, value_cache and out as
+    torch tensors of the case's dtype, block_tables / context_lens as int32 tensors, out_fp32, scale."""
+    z = np.load(GOLDEN / f"{name}.npz")
+    dtype = "bfloat16" if "bfloat16" in str(z["dtype"]) else "float16"
+    out = {k: _from_bits(z[k], dtype) for k in ("q", "key_cache", "value_cache", "out")}
+    out["block_tables"] = torch.from_numpy(z["block_tables"].copy())
+    out["context_lens"] = torch.from_numpy(z["context_lens"].copy())
+    out["out_fp32"] = torch.from_numpy(z["out_fp32"].copy())
+    out["scale"] = float(z["scale"])
+    return out

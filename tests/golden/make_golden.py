@@ -10,6 +10,11 @@ Run in a container that has the reference checkout (read-only) at ``$FLAG_ATTN_R
   ``recompute_mask_kernel``) executed by the Triton interpreter on CPU tensors.
 * ``dropout_masks.npz``: keep-masks from the reference's ``recompute_mask_kernel`` (interpreter).
 * ``split_heuristic.json``: ``num_splits_herustic`` evaluated on a grid of shapes.
+* ``paged_*.npz``: inputs and output of the reference's PyTorch paged attention
+  (``flag_attn.testing.paged_attention``, ``testing/paged.py:19-66``).
+
+``python tests/golden/make_golden.py paged`` (or any of ``split masks attention triton paged``)
+regenerates only the named groups.
 
 The fixtures travel with the repository; the tests never read the reference checkout.
 """
@@ -178,9 +183,39 @@ def gen_split_table():
     print("wrote split_heuristic", len(rows))
 
 
+PAGED_CASES = [
+    # name, seed, num_seqs, Hq, group, D, block, num_blocks, max_len, dtype
+    ("paged_mha_fp16", 11, 3, 2, 1, 64, 16, 12, 100, torch.float16),
+    ("paged_gqa8_fp16", 12, 2, 8, 8, 32, 16, 12, 70, torch.float16),
+    ("paged_gqa4_bf16", 13, 2, 4, 4, 128, 128, 5, 300, torch.bfloat16),
+]
+
+
+def gen_paged():
+    from flag_attn.testing.paged import attention as ref_paged
+    for name, seed, num_seqs, Hq, group, D, block, num_blocks, max_len, dtype in PAGED_CASES:
+        g = torch.Generator().manual_seed(seed)
+        Hkv = Hq // group
+        scale = D ** -0.5
+        q = ((torch.rand(num_seqs, Hq, D, generator=g) * 2 - 1) * scale * 8).to(dtype)
+        kc = ((torch.rand(num_blocks, Hkv, block, D, generator=g) * 2 - 1) * scale * 8).to(dtype)
+        vc = ((torch.rand(num_blocks, Hkv, block, D, generator=g) * 2 - 1)).to(dtype)
+        lens = torch.randint(1, max_len, (num_seqs,), generator=g, dtype=torch.int32)
+        lens[0] = max_len
+        per_seq = (max_len + block - 1) // block
+        tables = torch.randint(0, num_blocks, (num_seqs, per_seq), generator=g, dtype=torch.int32)
+        out = ref_paged(q, kc, vc, tables, lens, scale)
+        out32 = ref_paged(q.float(), kc.float(), vc.float(), tables, lens, scale)
+        np.savez_compressed(HERE / f"{name}.npz", q=bits(q), key_cache=bits(kc), value_cache=bits(vc),
+                            context_lens=lens.numpy(), block_tables=tables.numpy(), out=bits(out),
+                            out_fp32=out32.numpy(), scale=np.float32(scale),
+                            dtype=np.array(str(dtype)))
+        print("wrote", name)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
-    gen_split_table()
-    gen_masks()
-    gen_attention()
-    gen_triton_interp()
+    groups = {"split": gen_split_table, "masks": gen_masks, "attention": gen_attention,
+              "triton": gen_triton_interp, "paged": gen_paged}
+    for key in (sys.argv[1:] or list(groups)):
+        groups[key]()

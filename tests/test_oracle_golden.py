@@ -90,3 +90,19 @@ def test_philox_mask_statistics():
         mask = dropout_keep_mask(1, 2, 512, 612, p, 123456789, 123456789123456789)
         rate = 1.0 - mask.mean()
         assert abs(rate - p) / p < 0.01
+
+
+from conftest import PAGED_GOLDENS, load_paged_golden  # noqa: E402
+
+
+@pytest.mark.parametrize("name", PAGED_GOLDENS)
+def test_paged_oracle_matches_reference_fixture(name):
+    """oracle/paged.py against outputs of the reference's testing/paged.py (native dtype and fp32)."""
+    from oracle.paged import paged_attention
+    g = load_paged_golden(name)
+    got = paged_attention(g["q"], g["key_cache"], g["value_cache"], g["block_tables"], g["context_lens"], g["scale"])
+    assert got.dtype == g["out"].dtype
+    torch.testing.assert_close(got.float(), g["out"].float(), atol=2e-3, rtol=1e-2)
+    got32 = paged_attention(g["q"].float(), g["key_cache"].float(), g["value_cache"].float(), g["block_tables"],
+                            g["context_lens"], g["scale"])
+    torch.testing.assert_close(got32, g["out_fp32"], atol=1e-5, rtol=1e-5)
