@@ -1,7 +1,8 @@
 """Flash-decoding benchmark: one query token against a long key/value cache.
 
 Shapes follow the reference's ``benchmark/flash_decoding_benchmark.py`` (batch 2, 2048 / D heads,
-one query row, fp16, non-causal, D in {64, 128}, N = 2^9 .. 2^19) plus grouped-head decode shapes.
+one query row, fp16, non-causal, D in {64, 128}, N = 2^9 .. 2^19) plus grouped-head decode shapes
+and paged-cache decode (the shapes of ``benchmark/paged_benchmark.py``).
 The operation is a pure stream over K and V, so the figure of merit is the rate at which the K/V
 bytes are consumed, compared with the measured HBM copy bandwidth of the device.
 
@@ -20,7 +21,7 @@ from pathlib import Path
 
 import torch
 
-from . import _lib, check_device_status, flash_attention_split_kv
+from . import _lib, check_device_status, flash_attention_split_kv, paged_attention
 
 L2_BYTES = 126 * 2 ** 20
 FALLBACK_HBM_GBS = 6650.0
@@ -78,6 +79,26 @@ def run_case(B, Hq, Hk, M, N, D, dtype, iters, with_torch, device):
     return row
 
 
+def run_paged_case(num_seqs, Hq, group, D, block, context_len, dtype, iters, device):
+    """Shapes of the reference's ``benchmark/paged_benchmark.py`` (64 query heads, equal context
+    lengths, random block table), but with one distinct cache block per table entry so that the K/V
+    working set is what it would be in a real cache (and larger than L2) instead of 1000 shared blocks."""
+    Hkv = Hq // group
+    per_seq = -(-context_len // block)
+    num_blocks = num_seqs * per_seq
+    scale = D ** -0.5
+    q = torch.empty(num_seqs, Hq, D, dtype=dtype, device=device).uniform_(-scale, scale)
+    k_cache = torch.empty(num_blocks, Hkv, block, D, dtype=dtype, device=device).uniform_(-scale, scale)
+    v_cache = torch.empty_like(k_cache).uniform_(-scale, scale)
+    tables = torch.randperm(num_blocks, device=device).to(torch.int32).view(num_seqs, per_seq)
+    lens = torch.full((num_seqs,), context_len, dtype=torch.int32, device=device)
+    ms = _time_ms(lambda i: paged_attention(q, k_cache, v_cache, lens, tables, scale, context_len), iters)
+    kv_bytes = 2 * num_seqs * Hkv * context_len * D * 2
+    return {"num_seqs": num_seqs, "Hq": Hq, "Hkv": Hkv, "D": D, "block_size": block, "context_len": context_len,
+            "dtype": str(dtype)[6:], "us": round(ms * 1e3, 2), "kv_gbs": round(kv_bytes / ms / 1e6, 1),
+            "splits": int(_lib.load().b200attn_splitkv_num_splits(num_seqs, Hq, Hkv, 1, context_len, D, 0))}
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--json", action="store_true", help="one JSON object per line instead of a table")
@@ -114,6 +135,20 @@ def main():
             print(f"{tag:10s} B{B} Hq{Hq} Hkv{Hk} M{M} N{N:7d} D{D:3d} splits {row['splits']:3d}: "
                   f"{row['us']:9.1f} us  {row['kv_gbs']:7.0f} GB/s  {row['frac']:.2f} of {peak_kind} HBM peak"
                   f"{extra}", flush=True)
+    for group in (1, 8):
+        for block in (16, 128):
+            for context_len in (4096, 16384):
+                tag = f"paged-g{group}"
+                if args.case and not tag.startswith(args.case):
+                    continue
+                row = run_paged_case(32, 64, group, 128, block, context_len, torch.float16, args.iters, device)
+                row.update(case=tag, hbm_peak_gbs=peak, hbm_peak_kind=peak_kind, frac=round(row["kv_gbs"] / peak, 3))
+                if args.json:
+                    print(json.dumps(row), flush=True)
+                else:
+                    print(f"{tag:10s} seqs32 Hq64 Hkv{row['Hkv']} ctx{context_len:6d} D128 block{block:4d} splits "
+                          f"{row['splits']:3d}: {row['us']:9.1f} us  {row['kv_gbs']:7.0f} GB/s  {row['frac']:.2f} of "
+                          f"{peak_kind} HBM peak", flush=True)
     check_device_status(device)
 
 

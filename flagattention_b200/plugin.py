@@ -1,5 +1,5 @@
-"""Registers this implementation as the reference's ``flash_attention`` and
-``flash_attention_split_kv`` through the reference's own operator registry.
+"""Registers this implementation as the reference's ``flash_attention``,
+``flash_attention_split_kv`` and ``paged_attention`` through the reference's own operator registry.
 
 The reference resolves every public operator by name: ``flag_attn.__getattr__``
 (``src/flag_attn/__init__.py:123-135``) calls ``runtime.backend.resolve_operator``
@@ -7,8 +7,8 @@ The reference resolves every public operator by name: ``flag_attn.__getattr__``
 package's ``_OPERATOR_EXPORTS`` table (``op_registry.py:19-35``) and falls back to the generic
 Triton implementation. ``install()`` adds one row per operator to the NVIDIA vendor package's
 table, drops the registry's caches and the facade's cached callables, after which
-``flag_attn.flash_attention`` and ``flag_attn.flash_attention_split_kv`` are this package's
-functions. A declared override that fails to import is an error there, not a
+``flag_attn.flash_attention``, ``flag_attn.flash_attention_split_kv`` and
+``flag_attn.paged_attention`` are this package's functions. A declared override that fails to import is an error there, not a
 fallback, which matches this package having no fallback either.
 """
 from __future__ import annotations
@@ -21,6 +21,7 @@ TARGET = ("flagattention_b200.flash", "flash_attention")
 OPERATORS = {
     OPERATOR: TARGET,
     "flash_attention_split_kv": ("flagattention_b200.flash", "flash_attention_split_kv"),
+    "paged_attention": ("flagattention_b200.paged", "paged_attention"),
 }
 
 
@@ -41,8 +42,8 @@ def _drop_caches():
 
 
 def install(vendor: str = "nvidia") -> None:
-    """Make ``flag_attn.flash_attention`` and ``flag_attn.flash_attention_split_kv`` resolve to
-    this package's functions."""
+    """Make ``flag_attn.flash_attention``, ``flag_attn.flash_attention_split_kv`` and
+    ``flag_attn.paged_attention`` resolve to this package's functions."""
     pkg = _vendor_package(vendor)
     exports = dict(vars(pkg).get("_OPERATOR_EXPORTS", {}))
     exports.update(OPERATORS)
