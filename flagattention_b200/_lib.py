@@ -20,6 +20,8 @@ ERROR_NAMES = {0: "OK", -1: "EINVAL", -2: "EUNSUPPORTED", -3: "ECUDA", -4: "ETIM
 
 # Stage bits of b200attn_bwd_stages (include/b200attn.h).
 BWD_STAGE_PREP, BWD_STAGE_KV, BWD_STAGE_Q, BWD_STAGE_ALL, BWD_STAGE_UNFUSED = 1, 2, 4, 7, 8
+# Open ends of the visibility band (FwdParams.dist_min / dist_max).
+BAND_OPEN_MIN, BAND_OPEN_MAX = -(2 ** 31), 2 ** 31 - 1
 
 
 class Tensor4(Structure):
@@ -35,6 +37,7 @@ class FwdParams(Structure):
         ("sm_scale", c_float), ("dropout_p", c_float),
         ("seed", c_uint64), ("offset", c_uint64),
         ("status", c_void_p),
+        ("band", c_int32), ("dist_min", c_int32), ("dist_max", c_int32),
     ]
 
 
@@ -58,6 +61,7 @@ class BwdParams(Structure):
         ("sm_scale", c_float), ("dropout_p", c_float),
         ("seed", c_uint64), ("offset", c_uint64),
         ("status", c_void_p),
+        ("band", c_int32), ("dist_min", c_int32), ("dist_max", c_int32),
     ]
 
 
@@ -145,7 +149,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError here means the .so is stale
         fn.restype = restype
         fn.argtypes = argtypes
-    if lib.b200attn_abi_version() != 1:
+    if lib.b200attn_abi_version() != 2:
         raise RuntimeError("libb200attn.so ABI version mismatch; rebuild the library")
     _LIB = lib
     return lib

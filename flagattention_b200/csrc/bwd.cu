@@ -120,7 +120,7 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
   a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
   a.Mpad = pad128(p->M);
   a.groups = p->Hq / p->Hkv;
-  a.causal = p->causal ? 1 : 0;
+  a.causal = fold_band(p->causal != 0, p->band, p->dist_min, p->dist_max, &a.d_min, &a.d_max) ? 1 : 0;
   a.sm_scale = p->sm_scale;
   a.qk_scale = p->sm_scale * 1.4426950408889634f;
   a.drop = make_dropout_ctx(p->dropout_p, p->seed, p->offset);
@@ -198,7 +198,7 @@ static int run_total(const b200attn_total_params* p, float2* stats, cudaStream_t
   a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
   a.Mpad = pad128(p->M);
   a.groups = p->Hq / p->Hkv;
-  a.causal = p->causal ? 1 : 0;
+  a.causal = fold_band(p->causal != 0, 0, 0, 0, &a.d_min, &a.d_max) ? 1 : 0;
   a.sm_scale = p->sm_scale;
   a.qk_scale = p->sm_scale * 1.4426950408889634f;
   a.drop = make_dropout_ctx(0.f, 0, 0);

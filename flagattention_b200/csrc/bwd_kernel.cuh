@@ -61,7 +61,8 @@ struct BwdArgs {
   int64_t out2_sb, out2_sh, out2_sr;
   const float2* stats;  // [B, Hq, Mpad/2] float4 pairs, see above
   float* tot;           // MODE_TOTAL: [B, Hq, N]
-  int B, Hq, Hkv, M, N, Mpad, groups, causal;
+  int B, Hq, Hkv, M, N, Mpad, groups, causal;  // causal: some band limit below is finite
+  int d_min, d_max;  // visibility band: query m sees key n iff d_min <= m + (N - M) - n < d_max
   int n_zblocks, grid_chunk;  // grid order, see decode_block()
   float sm_scale, qk_scale;
   DropoutCtx drop;
@@ -154,7 +155,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
     n_heads = 1;
     hk = h_first / args.groups;
     col_lo = 0;
-    col_hi = args.causal ? min(args.N, max(0, P_SEQ + r0 + 128)) : args.N;
+    col_hi = (args.causal && args.d_min > -BAND_INF) ? min(args.N, max(0, P_SEQ + r0 + 128 - args.d_min)) : args.N;
+    if (args.causal && args.d_max < BAND_INF) col_lo = min(col_hi, (max(0, r0 + P_SEQ - args.d_max + 1) / STEP) * STEP);
   } else {
     r0 = bc.z * 128;                          // small n0 = most visible queries = longest first
     if constexpr (MODE == MODE_KV) {
@@ -166,8 +168,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       n_heads = 1;
       hk = h_first / args.groups;
     }
-    col_lo = args.causal ? (max(0, r0 - P_SEQ) / STEP) * STEP : 0;
-    col_hi = args.M;
+    col_lo = (args.causal && args.d_min > -BAND_INF) ? (max(0, r0 - P_SEQ + args.d_min) / STEP) * STEP : 0;
+    col_hi = (args.causal && args.d_max < BAND_INF) ? min(args.M, max(0, r0 + 127 - P_SEQ + args.d_max)) : args.M;
   }
   const int steps_per_head = col_hi > col_lo ? cdiv(col_hi - col_lo, STEP) : 0;
   const int T = steps_per_head * n_heads;
@@ -505,8 +507,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       // Does this step cross the causal boundary for some row of the block?
       bool diag = false;
       if (args.causal) {
-        if constexpr (MODE == MODE_Q) diag = col0 + HALF - 1 > r0 + P_SEQ;
-        else diag = col0 + P_SEQ < r0 + 127;
+        // d = m + P_SEQ - n ranges over [d_lo_blk, d_hi_blk] on this group's 128 x 32 block
+        int d_lo_blk, d_hi_blk;
+        if constexpr (MODE == MODE_Q) {
+          d_lo_blk = r0 + P_SEQ - (col0 + HALF - 1);
+          d_hi_blk = r0 + 127 + P_SEQ - col0;
+        } else {
+          d_lo_blk = col0 + P_SEQ - (r0 + 127);
+          d_hi_blk = col0 + HALF - 1 + P_SEQ - r0;
+        }
+        diag = d_lo_blk < args.d_min || d_hi_blk >= args.d_max;
       }
       const float4* stats4 = reinterpret_cast<const float4*>(sB + st * Sm::STAGE_BYTES + Sm::N_B * Sm::B_TILE_BYTES) +
                              wg * (HALF / 2);
@@ -529,11 +539,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         if (diag) {
           bool vis_a, vis_b;
           if constexpr (MODE == MODE_Q) {
-            vis_a = col0 + c <= row + P_SEQ;
-            vis_b = col0 + c + 1 <= row + P_SEQ;
+            const int d = row + P_SEQ - (col0 + c);
+            vis_a = d >= args.d_min && d < args.d_max;
+            vis_b = d - 1 >= args.d_min && d - 1 < args.d_max;
           } else {
-            vis_a = col0 + c + P_SEQ >= row;
-            vis_b = col0 + c + 1 + P_SEQ >= row;
+            const int d = col0 + c + P_SEQ - row;
+            vis_a = d >= args.d_min && d < args.d_max;
+            vis_b = d + 1 >= args.d_min && d + 1 < args.d_max;
           }
           p_a = vis_a ? p_a : 0.f;
           p_b = vis_b ? p_b : 0.f;

@@ -156,6 +156,22 @@ __device__ __forceinline__ float2 unpack2(uint32_t u) {
   }
 }
 
+// Band limits of the kernels (see FwdArgs::d_min): `causal` and the optional band of the C ABI
+// folded together. Returns whether any side is finite.
+__host__ inline bool fold_band(bool causal, int band, int dist_min, int dist_max, int* d_min, int* d_max) {
+  constexpr int INF = 1 << 30;
+  int lo = causal ? 0 : -INF, hi = INF;
+  if (band) {
+    const int bmin = dist_min < -INF ? -INF : (dist_min > INF ? INF : dist_min);
+    const int bmax = dist_max < -INF ? -INF : (dist_max > INF ? INF : dist_max);
+    if (bmin > lo) lo = bmin;
+    if (bmax < hi) hi = bmax;
+  }
+  *d_min = lo;
+  *d_max = hi;
+  return lo > -INF || hi < INF;
+}
+
 // 1-D grid order. Blocks are numbered so that (batch, head) pairs are visited in chunks of `chunk`
 // pairs; inside a chunk the row-block index z is the slow coordinate. With z sorted from the
 // longest block to the shortest this dispatches long (causal) blocks first, while a chunk's K/V

@@ -90,7 +90,7 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
   a.ring_stages = 0;
   a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
   a.groups = p->Hq / p->Hkv;
-  a.causal = p->causal ? 1 : 0;
+  a.causal = fold_band(p->causal != 0, p->band, p->dist_min, p->dist_max, &a.d_min, &a.d_max) ? 1 : 0;
   a.o_fp32 = p->o_dtype == B200ATTN_F32 ? 1 : 0;
   a.sm_scale = p->sm_scale;
   a.qk_scale = p->sm_scale * 1.4426950408889634f;
@@ -336,7 +336,7 @@ static int run_splitkv(const b200attn_splitkv_params* p, const PagedKV* paged, v
                   : p->D == 32 ? FwdSmem<32>::DUAL_STAGES : FwdSmem<16>::DUAL_STAGES;
   a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N;
   a.groups = p->Hq / p->Hkv;
-  a.causal = p->causal ? 1 : 0;
+  a.causal = fold_band(p->causal != 0, 0, 0, 0, &a.d_min, &a.d_max) ? 1 : 0;
   a.o_fp32 = 1;
   a.sm_scale = p->sm_scale;
   a.qk_scale = p->sm_scale * 1.4426950408889634f;

@@ -63,7 +63,11 @@ struct FwdArgs {
   const int32_t* context_lens;
   int block_shift;
   int B, Hq, Hkv, M, N, groups;
-  int causal, o_fp32;
+  int causal, o_fp32;               // causal: some band limit below is finite (enables the masking code)
+  // Visibility band: query m sees key n iff d_min <= m + (N - M) - n < d_max. Plain causal masking is
+  // d_min = 0; no mask is (-BAND_INF, BAND_INF); a sliding window or the two regions of piecewise
+  // attention set both.
+  int d_min, d_max;
   float sm_scale, qk_scale;
   DropoutCtx drop;
   int32_t* status;
@@ -91,6 +95,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 static constexpr float RESCALE_THRESHOLD = 8.0f;
+static constexpr int BAND_INF = 1 << 30;
 
 // Which of every 8 consecutive column pairs compute their exponential with the polynomial on the
 // FMA pipe instead of ex2.approx on the special-function unit (bit k = pair k). The smaller the head
@@ -145,7 +150,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const BlockCoord bc = decode_block(blockIdx.x, args.B * grid_heads, args.n_zblocks, args.grid_chunk);
   const int split = bc.z % args.num_splits;
   const int m_blk = args.n_zblocks / args.num_splits - 1 - bc.z / args.num_splits;  // longest first
-  const int j0 = split * args.tiles_per_split;  // first K/V tile of this CTA
+  const int j_split = split * args.tiles_per_split;  // first K/V tile of this CTA's split
   const int b = bc.bh / grid_heads;
   const int hk = packed ? bc.bh % grid_heads : (bc.bh % grid_heads) / args.groups;
   const int h = packed ? hk * args.groups : bc.bh % grid_heads;   // first (or only) query head
@@ -154,20 +159,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const int N_ctx = paged ? args.context_lens[b] : args.N;
   const int P_SEQ = N_ctx - args.M;
 
+  // First K/V tile the CTA streams: the split's first tile, or the first tile that the band's far
+  // edge lets the CTA's first query row see (the second query tile then meets one fully masked
+  // tile first, which costs one iteration).
+  int j0 = j_split;
+  if (args.causal && args.d_max < BAND_INF) j0 = max(j0, max(0, m0 + P_SEQ - args.d_max + 1) / BLOCK);
   // Number of K/V tiles each query tile visits.
   int n_tiles[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int mt = m0 + t * BLOCK;
     int hi = N_ctx;
-    if (args.causal) hi = min(N_ctx, max(0, P_SEQ + mt + BLOCK));
+    if (args.causal && args.d_min > -BAND_INF) hi = min(N_ctx, max(0, P_SEQ + mt + BLOCK - args.d_min));
     int n_full = mt < args.M ? cdiv(hi, BLOCK) : 0;
     if (packed) {
       // one tile holds every row of every head of the group: rows m = 0..M-1
-      const int hi_p = args.causal ? min(N_ctx, max(0, P_SEQ + args.M)) : N_ctx;
+      const int hi_p = (args.causal && args.d_min > -BAND_INF) ? min(N_ctx, max(0, P_SEQ + args.M - args.d_min)) : N_ctx;
       n_full = t == 0 ? cdiv(hi_p, BLOCK) : 0;
     }
-    n_tiles[t] = max(0, min(n_full, j0 + args.tiles_per_split) - j0);
+    n_tiles[t] = max(0, min(n_full, j_split + args.tiles_per_split) - j0);
   }
   if (dual) {
     const int n = n_tiles[0];
@@ -422,9 +432,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const int nt = n_tiles[t];
     const float qk_scale = args.qk_scale;
     // Keys n < lim are visible to this row.
-    const int lim = args.causal ? min(N_ctx, P_SEQ + m_glob + 1) : N_ctx;
+    const int lim = (args.causal && args.d_min > -BAND_INF) ? min(N_ctx, max(0, P_SEQ + m_glob + 1 - args.d_min)) : N_ctx;
+    // ... and keys n >= lo (the band's far edge).
+    const int lo = (args.causal && args.d_max < BAND_INF) ? max(0, P_SEQ + m_glob + 1 - args.d_max) : 0;
     // Tiles j with (j+1)*128 <= full_upto need no masking for any row of the tile.
-    const int full_upto = args.causal ? min(N_ctx, P_SEQ + (packed ? 0 : m0 + t * BLOCK) + 1) : N_ctx;
+    const int full_upto = (args.causal && args.d_min > -BAND_INF)
+                              ? min(N_ctx, max(0, P_SEQ + (packed ? 0 : m0 + t * BLOCK) + 1 - args.d_min)) : N_ctx;
+    // Tiles starting at or after full_from need no masking at the far edge for any row of the tile.
+    const int full_from = (args.causal && args.d_max < BAND_INF)
+                              ? max(0, P_SEQ + (packed ? args.M - 1 : m0 + t * BLOCK + BLOCK - 1) + 1 - args.d_max) : 0;
     const int split_out = dual ? 2 * split + t : split;
     uint64_t ctr_row = 0;
     if constexpr (DROPOUT) {
@@ -467,11 +483,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       tmem_ld32(tmem_s + 96, s + 96);
       tmem_wait_ld();
 
-      if ((jg + 1) * BLOCK > full_upto) {
+      if ((jg + 1) * BLOCK > full_upto || jg * BLOCK < full_from) {
         const int base = jg * BLOCK;
 #pragma unroll
         for (int i = 0; i < 128; ++i)
-          if (base + i >= lim) s[i] = 0xff800000u;  // -inf
+          if (base + i >= lim || base + i < lo) s[i] = 0xff800000u;  // -inf
       }
 
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define B200ATTN_ABI_VERSION 1
+#define B200ATTN_ABI_VERSION 2
 
 enum {
   B200ATTN_OK = 0,
@@ -57,6 +57,11 @@ typedef struct {
   uint64_t seed;       /* Philox key                                             */
   uint64_t offset;     /* Philox counter base                                    */
   int32_t* status;     /* optional device status word                            */
+  /* Optional visibility band (band != 0), on top of `causal`: key n is visible to query m iff
+   * dist_min <= m + (N - M) - n < dist_max. INT32_MIN / INT32_MAX leave that side open. Used for
+   * the two regions of piecewise attention (piecewise.py:39-205: distance >= w takes the second
+   * q/k pair) and usable as a sliding window. Rows with no visible key give o = 0, lse = -inf. */
+  int32_t band, dist_min, dist_max;
 } b200attn_fwd_params;
 
 int b200attn_fwd(const b200attn_fwd_params* p, void* stream);
@@ -116,6 +121,7 @@ typedef struct {
   float dropout_p;
   uint64_t seed, offset;
   int32_t* status;
+  int32_t band, dist_min, dist_max; /* visibility band as in b200attn_fwd_params */
 } b200attn_bwd_params;
 
 size_t b200attn_bwd_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t M, int32_t N,

@@ -74,3 +74,5 @@ def load_paged_golden(name: str) -> dict:
     out["out_fp32"] = torch.from_numpy(z["out_fp32"].copy())
     out["scale"] = float(z["scale"])
     return out
+
+PIECEWISE_GOLDENS = ["piecewise_causal_fp16", "piecewise_full_bf16", "piecewise_causal_larger_m"]

@@ -13,7 +13,10 @@ Run in a container that has the reference checkout (read-only) at ``$FLAG_ATTN_R
 * ``paged_*.npz``: inputs and output of the reference's PyTorch paged attention
   (``flag_attn.testing.paged_attention``, ``testing/paged.py:19-66``).
 
-``python tests/golden/make_golden.py paged`` (or any of ``split masks attention triton paged``)
+* ``piecewise_*.npz``: inputs, outputs and autograd gradients of the reference's PyTorch piecewise
+  attention (``flag_attn.testing.piecewise_attention``, ``testing/piecewise.py:19-49``).
+
+``python tests/golden/make_golden.py paged`` (or any of ``split masks attention triton paged piecewise``)
 regenerates only the named groups.
 
 The fixtures travel with the repository; the tests never read the reference checkout.
@@ -213,9 +216,39 @@ def gen_paged():
         print("wrote", name)
 
 
+PIECEWISE_CASES = [
+    # name, seed, B, H, M, N, D, dtype, causal, w
+    ("piecewise_causal_fp16", 21, 1, 2, 136, 200, 32, torch.float16, True, 68),
+    ("piecewise_full_bf16", 22, 1, 2, 300, 180, 64, torch.bfloat16, False, 210),
+    ("piecewise_causal_larger_m", 23, 1, 1, 260, 129, 16, torch.bfloat16, True, 195),
+]
+
+
+def gen_piecewise():
+    from flag_attn.testing.piecewise import attention as ref_piecewise
+    for name, seed, B, H, M, N, D, dtype, causal, w in PIECEWISE_CASES:
+        g = torch.Generator().manual_seed(seed)
+        q1, q2, do = (torch.randn(B, H, M, D, generator=g).to(dtype) for _ in range(3))
+        k1, k2, v = (torch.randn(B, H, N, D, generator=g).to(dtype) for _ in range(3))
+        leaves = [t.clone().requires_grad_(True) for t in (q1, k1, q2, k2, v)]
+        o32 = ref_piecewise(*leaves, w, causal, upcast=True)
+        g32 = torch.autograd.grad(o32, leaves, do)
+        leaves_low = [t.clone().requires_grad_(True) for t in (q1, k1, q2, k2, v)]
+        o_low = ref_piecewise(*leaves_low, w, causal, upcast=False)
+        g_low = torch.autograd.grad(o_low, leaves_low, do)
+        arrays = dict(q1=bits(q1), k1=bits(k1), q2=bits(q2), k2=bits(k2), v=bits(v), do=bits(do),
+                      o_upcast=bits(o32.detach()), o_native=bits(o_low.detach()),
+                      meta=np.array(json.dumps(dict(B=B, H=H, M=M, N=N, D=D, dtype=str(dtype)[6:], causal=causal, w=w))))
+        for nm, a, b_ in zip(("dq1", "dk1", "dq2", "dk2", "dv"), g32, g_low):
+            arrays[nm + "_upcast"] = bits(a)
+            arrays[nm + "_native"] = bits(b_)
+        np.savez_compressed(HERE / f"{name}.npz", **arrays)
+        print("wrote", name)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     groups = {"split": gen_split_table, "masks": gen_masks, "attention": gen_attention,
-              "triton": gen_triton_interp, "paged": gen_paged}
+              "triton": gen_triton_interp, "paged": gen_paged, "piecewise": gen_piecewise}
     for key in (sys.argv[1:] or list(groups)):
         groups[key]()

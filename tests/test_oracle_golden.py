@@ -106,3 +106,22 @@ def test_paged_oracle_matches_reference_fixture(name):
     got32 = paged_attention(g["q"].float(), g["key_cache"].float(), g["value_cache"].float(), g["block_tables"],
                             g["context_lens"], g["scale"])
     torch.testing.assert_close(got32, g["out_fp32"], atol=1e-5, rtol=1e-5)
+
+
+from conftest import PIECEWISE_GOLDENS  # noqa: E402
+
+
+@pytest.mark.parametrize("name", PIECEWISE_GOLDENS)
+def test_piecewise_oracle_matches_reference_fixture(name):
+    """oracle/piecewise.py against outputs and autograd gradients of the reference's
+    testing/piecewise.py: same formula on the same CPU, so bit for bit."""
+    from oracle.piecewise import piecewise_attention
+    g = load_golden(name)
+    meta = g["meta"]
+    for mode, upcast in (("upcast", True), ("native", False)):
+        leaves = [g[k].clone().requires_grad_(True) for k in ("q1", "k1", "q2", "k2", "v")]
+        o = piecewise_attention(*leaves, meta["w"], meta["causal"], upcast=upcast)
+        assert torch.equal(o, g[f"o_{mode}"])
+        grads = torch.autograd.grad(o, leaves, g["do"])
+        for nm, got in zip(("dq1", "dk1", "dq2", "dk2", "dv"), grads):
+            assert torch.equal(got, g[f"{nm}_{mode}"]), (name, mode, nm)
