@@ -27,7 +27,7 @@ from pathlib import Path
 
 import torch
 
-from . import check_device_status, flash_attention
+from . import check_device_status, flash_attention, piecewise_attention
 
 SPEC_PEAK_TFLOPS = 2250.0
 LOG_PATH_ENV = "FLAG_ATTN_BENCHMARK_LOG_PATH"
@@ -66,19 +66,35 @@ def flops(n_ctx, head_dim, causal, mode):
     return f * (0.5 if causal else 1.0)
 
 
-def measure(provider, n_ctx, head_dim, causal, mode, dtype, device, warmup, iters):
+def _torch_piecewise(q1, k1, q2, k2, v, w, causal):
+    m, n = q1.shape[2], k1.shape[2]
+    dist = (torch.arange(m, device=q1.device).unsqueeze(-1) + (n - m)) - torch.arange(n, device=q1.device)
+    s = torch.where(dist >= w, q2 @ k2.transpose(2, 3), q1 @ k1.transpose(2, 3)) * (1.0 / math.sqrt(q1.shape[-1]))
+    if causal:
+        s = s.masked_fill(dist < 0, float("-inf"))
+    return torch.softmax(s.float(), -1).to(v.dtype) @ v
+
+
+def measure(provider, n_ctx, head_dim, causal, mode, dtype, device, warmup, iters, op="flash_attention"):
     batch, heads = 32768 // n_ctx, 2048 // head_dim
     need_grad = mode == "bwd"
-    q, k, v = (torch.randn(batch, heads, n_ctx, head_dim, dtype=dtype, device=device, requires_grad=need_grad)
-               for _ in range(3))
-    if provider == "ours":
-        fn = lambda: flash_attention(q, k, v, causal=causal)  # noqa: E731
+    n_inputs = 3 if op == "flash_attention" else 5
+    leaves = tuple(torch.randn(batch, heads, n_ctx, head_dim, dtype=dtype, device=device, requires_grad=need_grad)
+                   for _ in range(n_inputs))
+    if op == "flash_attention":
+        q, k, v = leaves
+        fn = (lambda: flash_attention(q, k, v, causal=causal)) if provider == "ours" else \
+             (lambda: _torch_attention(q, k, v, causal))
     else:
-        fn = lambda: _torch_attention(q, k, v, causal)  # noqa: E731
+        # the reference's piecewise benchmark: threshold at half the sequence (piecewise_benchmark.py:65)
+        q1, k1, q2, k2, v = leaves
+        w = n_ctx // 2
+        fn = (lambda: piecewise_attention(q1, k1, q2, k2, v, w, causal=causal)) if provider == "ours" else \
+             (lambda: _torch_piecewise(q1, k1, q2, k2, v, w, causal))
     if need_grad:
         o = fn()
         do = torch.randn_like(o)
-        fn = lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True)  # noqa: E731
+        fn = lambda: torch.autograd.grad(o, leaves, do, retain_graph=True)  # noqa: E731
     return _time_ms(fn, warmup, iters)
 
 
@@ -100,6 +116,8 @@ def main():
     ap.add_argument("--min-log2-n", type=int, default=9)
     ap.add_argument("--max-log2-n", type=int, default=15)
     ap.add_argument("--quick", action="store_true", help="D=128, bf16, causal only")
+    ap.add_argument("--op", default="flash_attention", choices=["flash_attention", "piecewise_attention"],
+                    help="piecewise_attention: the shapes of benchmark/piecewise_benchmark.py, same FLOP formula")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
@@ -116,13 +134,15 @@ def main():
                 for head_dim in dims:
                     for log2n in range(args.min_log2_n, args.max_log2_n + 1):
                         n_ctx = 2 ** log2n
-                        ms = measure("ours", n_ctx, head_dim, causal, mode, dtype, device, args.warmup, args.iters)
+                        ms = measure("ours", n_ctx, head_dim, causal, mode, dtype, device, args.warmup, args.iters,
+                                     args.op)
                         base = None
                         # scores + probabilities of the plain formula: batch*heads*N^2*(2+4+2) bytes
-                        if not args.no_torch and (32768 // n_ctx) * (2048 // head_dim) * n_ctx * n_ctx * 8 <= 40e9:
+                        per_score = 8 if args.op == "flash_attention" else 14  # piecewise keeps two score matrices
+                        if not args.no_torch and (32768 // n_ctx) * (2048 // head_dim) * n_ctx * n_ctx * per_score <= 40e9:
                             try:
                                 base = measure("torch", n_ctx, head_dim, causal, mode, dtype, device, 2,
-                                               max(3, args.iters // 4))
+                                               max(3, args.iters // 4), args.op)
                             except torch.OutOfMemoryError:
                                 base = None
                                 torch.cuda.empty_cache()
@@ -137,7 +157,7 @@ def main():
                         print(f"{str(dtype)[6:]:8s} {mode} causal={int(causal)} D={head_dim:3d} N_CTX={n_ctx:6d}: "
                               f"{ms:8.3f} ms {tf:7.1f} TFLOP/s"
                               + (f"   torch {base:9.3f} ms  x{base / ms:6.1f}" if base else ""), flush=True)
-        emit({"level": "comprehensive", "op_name": "flash_attention", "dtype": str(dtype), "mode": "kernel",
+        emit({"level": "comprehensive", "op_name": args.op, "dtype": str(dtype), "mode": "kernel",
               "result": rows, "baseline": None if args.no_torch else "torch"})
     check_device_status(device)
 

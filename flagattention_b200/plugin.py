@@ -1,5 +1,6 @@
 """Registers this implementation as the reference's ``flash_attention``,
-``flash_attention_split_kv`` and ``paged_attention`` through the reference's own operator registry.
+``flash_attention_split_kv``, ``paged_attention`` and ``piecewise_attention`` through the reference's
+own operator registry.
 
 The reference resolves every public operator by name: ``flag_attn.__getattr__``
 (``src/flag_attn/__init__.py:123-135``) calls ``runtime.backend.resolve_operator``
@@ -22,6 +23,7 @@ OPERATORS = {
     OPERATOR: TARGET,
     "flash_attention_split_kv": ("flagattention_b200.flash", "flash_attention_split_kv"),
     "paged_attention": ("flagattention_b200.paged", "paged_attention"),
+    "piecewise_attention": ("flagattention_b200.piecewise", "piecewise_attention"),
 }
 
 

@@ -17,7 +17,8 @@ def fake_flag_attn(tmp_path, monkeypatch):
         from . import runtime
         _OPERATOR_EXPORTS = {"flash_attention": ("flag_attn.flash", "attention"),
                              "flash_attention_split_kv": ("flag_attn.split_kv", "attention"),
-                             "paged_attention": ("flag_attn.paged", "attention")}
+                             "paged_attention": ("flag_attn.paged", "attention"),
+                             "piecewise_attention": ("flag_attn.piecewise", "attention")}
         def __getattr__(name):
             module_name, attribute_name = _OPERATOR_EXPORTS[name]
             value = runtime.backend.resolve_operator(name, module_name, attribute_name)
@@ -27,6 +28,7 @@ def fake_flag_attn(tmp_path, monkeypatch):
     (root / "flash.py").write_text("def attention(*a, **k):\n    return 'generic'\n")
     (root / "split_kv.py").write_text("def attention(*a, **k):\n    return 'generic-split'\n")
     (root / "paged.py").write_text("def attention(*a, **k):\n    return 'generic-paged'\n")
+    (root / "piecewise.py").write_text("def attention(*a, **k):\n    return 'generic-piecewise'\n")
     (root / "runtime" / "__init__.py").write_text(textwrap.dedent('''
         from . import backend
         class _Dev:
@@ -70,7 +72,9 @@ def test_install_and_uninstall(fake_flag_attn):
     assert fa.flash_attention is flash_attention
     assert fa.flash_attention_split_kv is flash_attention_split_kv
     assert fa.paged_attention is paged_attention
+    assert fa.piecewise_attention.__module__ == "flagattention_b200.piecewise"
     plugin.uninstall()
+    assert fa.piecewise_attention() == "generic-piecewise"
     assert fa.paged_attention() == "generic-paged"
     assert fa.flash_attention() == "generic"
     assert fa.flash_attention_split_kv() == "generic-split"
