@@ -31,7 +31,7 @@ template <int D, int O_KIND, bool DO_BF16>
 __global__ void __launch_bounds__(256)
 delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __restrict__ delta,
              int64_t o_sb, int64_t o_sh, int64_t o_sm, int64_t do_sb, int64_t do_sh, int64_t do_sm, int B,
-             int H, int M) {
+             int H, int M, float* __restrict__ zero_rows) {
   constexpr int VEC = 8;                 // elements per lane per step
   constexpr int LANES = D / VEC;         // lanes that carry data for one row (2..16)
   constexpr int ROWS_PER_WARP = 32 / LANES;
@@ -74,6 +74,13 @@ delta_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __
     }
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc = fmaf(ov[i], gv[i], acc);
+    // Optional: clear the matching 8 elements of a contiguous fp32 [B, H, M, D] array (the dQ
+    // accumulator of the fused backward), saving a separate pass over it.
+    if (zero_rows != nullptr) {
+      float4* z = reinterpret_cast<float4*>(zero_rows + row_id * D + col);
+      z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
 #pragma unroll
   for (int s = LANES / 2; s >= 1; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
@@ -119,7 +126,7 @@ int launch_stats(const float* lse, const float* delta, float2* stats, int B, int
 
 template <int D>
 static int launch_delta(const b200attn_tensor* o, int o_dtype, const b200attn_tensor* d_o, int do_dtype,
-                        float* delta, int B, int H, int M, cudaStream_t stream) {
+                        float* delta, int B, int H, int M, cudaStream_t stream, float* zero_rows) {
   constexpr int ROWS_PER_WARP = 32 / (D / 8);
   const int64_t total = static_cast<int64_t>(B) * H * M;
   const int64_t warps = (total + ROWS_PER_WARP - 1) / ROWS_PER_WARP;
@@ -127,7 +134,7 @@ static int launch_delta(const b200attn_tensor* o, int o_dtype, const b200attn_te
 #define B200ATTN_DELTA(OK, DB)                                                                        \
   delta_kernel<D, OK, DB><<<blocks, 256, 0, stream>>>(o->ptr, d_o->ptr, delta, o->stride[0],          \
                                                       o->stride[1], o->stride[2], d_o->stride[0],    \
-                                                      d_o->stride[1], d_o->stride[2], B, H, M)
+                                                      d_o->stride[1], d_o->stride[2], B, H, M, zero_rows)
   const bool db = do_dtype == B200ATTN_BF16;
   if (o_dtype == B200ATTN_F32) { if (db) B200ATTN_DELTA(B200ATTN_F32, true); else B200ATTN_DELTA(B200ATTN_F32, false); }
   else if (o_dtype == B200ATTN_BF16) { if (db) B200ATTN_DELTA(B200ATTN_BF16, true); else B200ATTN_DELTA(B200ATTN_BF16, false); }
@@ -219,10 +226,9 @@ extern "C" int b200attn_dropout_mask(uint8_t* mask, int32_t B, int32_t H, int32_
   return B200ATTN_OK;
 }
 
-extern "C" int b200attn_bwd_delta(const b200attn_tensor* o, int32_t o_dtype, const b200attn_tensor* d_o,
-                                  int32_t do_dtype, float* delta, int32_t B, int32_t H, int32_t M,
-                                  int32_t D, void* stream) {
-  using namespace b200attn;
+namespace b200attn {
+int bwd_delta(const b200attn_tensor* o, int32_t o_dtype, const b200attn_tensor* d_o, int32_t do_dtype,
+              float* delta, int32_t B, int32_t H, int32_t M, int32_t D, void* stream, float* zero_rows) {
   if (delta == nullptr || B <= 0 || H <= 0 || M <= 0) {
     set_error("bwd_delta: bad argument");
     return B200ATTN_EINVAL;
@@ -237,14 +243,21 @@ extern "C" int b200attn_bwd_delta(const b200attn_tensor* o, int32_t o_dtype, con
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (D) {
-    case 16: return launch_delta<16>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s);
-    case 32: return launch_delta<32>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s);
-    case 64: return launch_delta<64>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s);
-    case 128: return launch_delta<128>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s);
+    case 16: return launch_delta<16>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s, zero_rows);
+    case 32: return launch_delta<32>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s, zero_rows);
+    case 64: return launch_delta<64>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s, zero_rows);
+    case 128: return launch_delta<128>(o, o_dtype, d_o, do_dtype, delta, B, H, M, s, zero_rows);
     default:
       set_error("bwd_delta: head dimension %d not in {16, 32, 64, 128}", D);
       return B200ATTN_EINVAL;
   }
+}
+}  // namespace b200attn
+
+extern "C" int b200attn_bwd_delta(const b200attn_tensor* o, int32_t o_dtype, const b200attn_tensor* d_o,
+                                  int32_t do_dtype, float* delta, int32_t B, int32_t H, int32_t M,
+                                  int32_t D, void* stream) {
+  return b200attn::bwd_delta(o, o_dtype, d_o, do_dtype, delta, B, H, M, D, stream, nullptr);
 }
 
 extern "C" int b200attn_merge_partial(float* o_acc, float* lse_acc, const float* o_part,

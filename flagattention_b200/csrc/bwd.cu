@@ -159,7 +159,9 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
     float* dq_acc = reinterpret_cast<float*>(stats + static_cast<size_t>(p->B) * p->Hq * a.Mpad);
     const int64_t n_acc = static_cast<int64_t>(p->B) * p->Hq * p->M * D;
     if (stages & B200ATTN_BWD_STAGE_KV) {
-      B200ATTN_CUDA_OK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(n_acc) * sizeof(float), stream));
+      // (cleared by the preprocess when that ran in this call)
+      if (!(stages & B200ATTN_BWD_STAGE_PREP))
+        B200ATTN_CUDA_OK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(n_acc) * sizeof(float), stream));
       kv.fused = true;
       kv.args.dq_acc = dq_acc;
       if ((rc = dispatch(D, kv))) return rc;
@@ -268,7 +270,11 @@ extern "C" int b200attn_bwd_stages(const b200attn_bwd_params* p, void* stream_, 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   float2* stats = static_cast<float2*>(p->workspace);
   if (stages & B200ATTN_BWD_STAGE_PREP) {
-    rc = b200attn_bwd_delta(&p->o, p->o_dtype, &p->d_o, p->dtype, p->delta, p->B, p->Hq, p->M, p->D, stream_);
+    // When the fused pass follows in the same call, the preprocess also clears its dQ accumulator.
+    float* zero_rows = nullptr;
+    if (fused_dq(p->D, stages) && (stages & B200ATTN_BWD_STAGE_KV))
+      zero_rows = reinterpret_cast<float*>(stats + static_cast<size_t>(p->B) * p->Hq * pad128(p->M));
+    rc = bwd_delta(&p->o, p->o_dtype, &p->d_o, p->dtype, p->delta, p->B, p->Hq, p->M, p->D, stream_, zero_rows);
     if (rc) return rc;
     rc = launch_stats(p->lse, p->delta, stats, p->B, p->Hq, p->M, pad128(p->M), stream);
     if (rc) return rc;

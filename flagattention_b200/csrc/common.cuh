@@ -34,6 +34,9 @@ int check_tma_operand(const b200attn_tensor& t, int elem_bytes, const char* name
 
 // Writes the padded per-query statistics the backward / total-attention kernels stream
 // (aux_kernels.cu). `delta` may be null (total attention).
+// delta[b,h,m] = sum_d o*do; optionally also clears a contiguous fp32 [B, H, M, D] array.
+int bwd_delta(const b200attn_tensor* o, int32_t o_dtype, const b200attn_tensor* d_o, int32_t do_dtype,
+              float* delta, int32_t B, int32_t H, int32_t M, int32_t D, void* stream, float* zero_rows);
 int launch_stats(const float* lse, const float* delta, float2* stats, int B, int H, int M, int Mpad,
                  cudaStream_t stream);
 
