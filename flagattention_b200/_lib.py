@@ -38,6 +38,7 @@ class FwdParams(Structure):
         ("seed", c_uint64), ("offset", c_uint64),
         ("status", c_void_p),
         ("band", c_int32), ("dist_min", c_int32), ("dist_max", c_int32),
+        ("keep_mask", c_void_p),
     ]
 
 
@@ -62,6 +63,7 @@ class BwdParams(Structure):
         ("seed", c_uint64), ("offset", c_uint64),
         ("status", c_void_p),
         ("band", c_int32), ("dist_min", c_int32), ("dist_max", c_int32),
+        ("keep_mask", c_void_p),
     ]
 
 
@@ -114,6 +116,7 @@ SYMBOLS = {
                                      c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200attn_dropout_mask": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_float, c_uint64,
                                         c_uint64, c_void_p]),
+    "b200attn_keep_mask_bytes": (c_size_t, [c_int32] * 4),
     "b200attn_fwd_splitkv": (c_int32, [POINTER(SplitKVParams), c_void_p]),
     "b200attn_splitkv_num_splits": (c_int32, [c_int32] * 7),
     "b200attn_paged_attention": (c_int32, [POINTER(PagedParams), c_void_p]),

@@ -124,6 +124,10 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
   a.sm_scale = p->sm_scale;
   a.qk_scale = p->sm_scale * 1.4426950408889634f;
   a.drop = make_dropout_ctx(p->dropout_p, p->seed, p->offset);
+  if (p->dropout_p > 0.f && p->keep_mask != nullptr) {
+    a.drop.keep_mask = const_cast<uint32_t*>(p->keep_mask);
+    a.drop.mask_words = cdiv(p->N, 32);
+  }
   a.status = p->status;
 #ifdef B200ATTN_TIMING
   a.trace = trace_buffer();

@@ -485,11 +485,28 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       if constexpr (DROPOUT) {
         const uint64_t head_base = args.drop.offset +
                                    (static_cast<uint64_t>(b) * args.Hq + h) * args.M * static_cast<uint64_t>(args.N);
-        if constexpr (MODE == MODE_Q)
+        if (args.drop.keep_mask != nullptr) {
+          // decisions cached by the forward (see DropoutCtx::keep_mask)
+          const uint32_t* mk = args.drop.keep_mask + (static_cast<int64_t>(b) * args.Hq + h) * args.drop.mask_words * args.M;
+          if constexpr (MODE == MODE_Q) {
+            keep_bits = row < args.M ? mk[static_cast<int64_t>(col0 >> 5) * args.M + row] : 0u;
+          } else {
+            // the warp's 32 key rows share one word index; lane c fetches query col0 + c's word, then
+            // every lane picks its own key's bit out of each
+            const int wi = (r0 + (warp & 3) * 32) >> 5;
+            const uint32_t wq = (col0 + lane < args.M && wi < args.drop.mask_words)
+                                    ? mk[static_cast<int64_t>(wi) * args.M + col0 + lane] : 0u;
+            keep_bits = 0u;
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              keep_bits |= ((__shfl_sync(0xffffffffu, wq, c) >> lane) & 1u) << c;
+          }
+        } else if constexpr (MODE == MODE_Q) {
           keep_bits = dropout_keep_word(args.drop, head_base + static_cast<uint64_t>(row) * args.N + col0);
-        else
+        } else {
           keep_bits = dropout_keep_word_strided(args.drop, head_base + static_cast<uint64_t>(col0) * args.N + row,
                                                 static_cast<uint64_t>(args.N));
+        }
       }
       {
         const bool w = wait(&t_full[buf], (i >> 1) & 1);

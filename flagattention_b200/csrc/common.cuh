@@ -80,6 +80,12 @@ struct DropoutCtx {
   int32_t keep_threshold;
   uint32_t wide;
   float inv_keep;  // 1 / (1 - p)
+  // Optional cache of the keep decisions, written by the forward and read by the backward instead of
+  // re-evaluating Philox: bit i of word keep_mask[((b * Hq + h) * mask_words + w) * M + m] says whether
+  // (query m, key 32 * w + i) is kept. Word-major, so that both a thread per query row (forward,
+  // dQ kernel) and 32 lanes holding 32 consecutive queries (dK/dV kernel) touch consecutive words.
+  uint32_t* keep_mask;
+  int mask_words;  // ceil(N / 32)
 };
 
 __host__ inline DropoutCtx make_dropout_ctx(float p, uint64_t seed, uint64_t offset) {
@@ -90,6 +96,8 @@ __host__ inline DropoutCtx make_dropout_ctx(float p, uint64_t seed, uint64_t off
   c.keep_threshold = dropout_keep_threshold(p);
   c.wide = offset >= (1ull << 31) ? 1u : 0u;
   c.inv_keep = 1.0f / (1.0f - p);
+  c.keep_mask = nullptr;
+  c.mask_words = 0;
   return c;
 }
 

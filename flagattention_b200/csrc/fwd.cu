@@ -95,6 +95,10 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
   a.sm_scale = p->sm_scale;
   a.qk_scale = p->sm_scale * 1.4426950408889634f;
   a.drop = make_dropout_ctx(p->dropout_p, p->seed, p->offset);
+  if (p->dropout_p > 0.f && p->keep_mask != nullptr) {
+    a.drop.keep_mask = p->keep_mask;
+    a.drop.mask_words = cdiv(p->N, 32);
+  }
   a.status = p->status;
   a.n_zblocks = cdiv(p->M, 256);
   a.grid_chunk = grid_chunk(a.groups, 4ll * p->N * p->D, a.causal != 0);
@@ -359,6 +363,11 @@ static int run_splitkv(const b200attn_splitkv_params* p, const PagedKV* paged, v
 }
 
 }  // namespace b200attn
+
+extern "C" size_t b200attn_keep_mask_bytes(int32_t B, int32_t Hq, int32_t M, int32_t N) {
+  if (B <= 0 || Hq <= 0 || M <= 0 || N <= 0) return 0;
+  return static_cast<size_t>(B) * Hq * ((N + 31) / 32) * M * sizeof(uint32_t);
+}
 
 extern "C" int b200attn_fwd_splitkv(const b200attn_splitkv_params* p, void* stream) {
   return b200attn::run_splitkv(p, nullptr, stream);

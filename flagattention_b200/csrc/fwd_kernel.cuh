@@ -463,6 +463,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const uint64_t base = ctr_row + static_cast<uint64_t>(jg * BLOCK);
 #pragma unroll
         for (int w = 0; w < 4; ++w) keep_bits[w] = dropout_keep_word(args.drop, base + 32 * w);
+        if (args.drop.keep_mask != nullptr && m_glob < args.M) {
+          uint32_t* mk = args.drop.keep_mask +
+                         ((static_cast<int64_t>(b) * args.Hq + h_row) * args.drop.mask_words + jg * 4) * args.M + m_glob;
+#pragma unroll
+          for (int w = 0; w < 4; ++w)
+            if (jg * 4 + w < args.drop.mask_words) mk[static_cast<int64_t>(w) * args.M] = keep_bits[w];
+        }
       }
       {
         const bool w = wait(&s_full[t], j & 1);

@@ -19,6 +19,8 @@ from .split_kv import choose_num_splits
 __all__ = ["flash_attention", "FlashAttentionFunction", "check_device_status"]
 
 _SUPPORTED_HEAD_DIMS = (16, 32, 64, 128)
+# Largest dropout keep-decision cache (bytes, one bit per attention score) handed from forward to backward.
+_KEEP_MASK_LIMIT = 1 << 30
 _status_words: dict[int, torch.Tensor] = {}
 
 
@@ -182,6 +184,7 @@ class FlashAttentionFunction(torch.autograd.Function):
             num_splits = choose_num_splits(B, H, M, N, num_sms)
             stream = _lib.current_stream_ptr(device)
             status = _status_word(device)
+            keep_mask = None
             if num_splits > 1:
                 assert not is_dropout, "Cannot apply dropout with splitkv."
                 o, L = _split_kv_forward(lib, q, k, v, bool(causal), float(sm_scale), num_sms, stream,
@@ -195,11 +198,18 @@ class FlashAttentionFunction(torch.autograd.Function):
                 o = torch.empty_like(q, dtype=out_dtype)
                 if _tma_ready(o) is not o:
                     o = torch.empty(q.shape, dtype=out_dtype, device=device)
+                # With dropout, the keep decisions (one bit per score) are kept for the backward when
+                # they fit in _KEEP_MASK_LIMIT bytes: re-evaluating Philox there costs more than the
+                # rest of the backward. Larger problems recompute, as the reference always does.
+                if is_dropout and any(ctx.needs_input_grad[:3]):
+                    mask_bytes = lib.b200attn_keep_mask_bytes(B, H, M, N)
+                    if mask_bytes <= _KEEP_MASK_LIMIT:
+                        keep_mask = torch.empty(mask_bytes // 4, dtype=torch.int32, device=device)
                 fp = _lib.FwdParams(
                     _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), L.data_ptr(),
                     B, H, Hk, M, N, D, _lib.dtype_code(q.dtype), _lib.dtype_code(out_dtype),
                     int(bool(causal)), float(sm_scale), dropout_p, as_u64(seed), as_u64(offset),
-                    status.data_ptr())
+                    status.data_ptr(), 0, 0, 0, keep_mask.data_ptr() if keep_mask is not None else None)
                 _lib.check(lib.b200attn_fwd(fp, stream), "b200attn_fwd")
 
             tot_attn = None
@@ -214,6 +224,7 @@ class FlashAttentionFunction(torch.autograd.Function):
                 _lib.check(lib.b200attn_total_attention(tp, stream), "b200attn_total_attention")
 
         ctx.save_for_backward(q, k, v, o, L)
+        ctx.keep_mask = keep_mask
         ctx.sm_scale = sm_scale
         ctx.causal = bool(causal)
         ctx.dropout_p = dropout_p
@@ -259,7 +270,8 @@ class FlashAttentionFunction(torch.autograd.Function):
                 L.data_ptr(), delta.data_ptr(), workspace.data_ptr(),
                 B, H, Hk, M, N, D, _lib.dtype_code(q.dtype), _lib.dtype_code(o.dtype),
                 int(ctx.causal), float(ctx.sm_scale), float(ctx.dropout_p),
-                as_u64(ctx.seed), as_u64(ctx.offset), status.data_ptr())
+                as_u64(ctx.seed), as_u64(ctx.offset), status.data_ptr(), 0, 0, 0,
+                ctx.keep_mask.data_ptr() if ctx.keep_mask is not None else None)
             # At D = 128 and 64 the library produces dQ inside the dK/dV pass, summing the key blocks'
             # contributions by fp32 reductions in global memory: faster, but the summation order (and
             # so the last bit of dQ) can differ between runs. torch.use_deterministic_algorithms(True)

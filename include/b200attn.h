@@ -62,7 +62,14 @@ typedef struct {
    * the two regions of piecewise attention (piecewise.py:39-205: distance >= w takes the second
    * q/k pair) and usable as a sliding window. Rows with no visible key give o = 0, lse = -inf. */
   int32_t band, dist_min, dist_max;
+  /* Optional (dropout_p > 0): b200attn_keep_mask_bytes() bytes that receive the keep decisions, one
+   * bit per (query, key), for b200attn_bwd to reuse instead of re-evaluating Philox (the reference
+   * recomputes them in both backward kernels, flash.py:660-664,846-850). NULL = not stored. */
+  uint32_t* keep_mask;
 } b200attn_fwd_params;
+
+/* Size of the keep-decision cache: B * Hq * ceil(N / 32) * M words. */
+size_t b200attn_keep_mask_bytes(int32_t B, int32_t Hq, int32_t M, int32_t N);
 
 int b200attn_fwd(const b200attn_fwd_params* p, void* stream);
 
@@ -122,6 +129,7 @@ typedef struct {
   uint64_t seed, offset;
   int32_t* status;
   int32_t band, dist_min, dist_max; /* visibility band as in b200attn_fwd_params */
+  const uint32_t* keep_mask;        /* cache written by b200attn_fwd for the same call, or NULL */
 } b200attn_bwd_params;
 
 size_t b200attn_bwd_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t M, int32_t N,

@@ -290,3 +290,36 @@ def test_return_conventions_and_rng_untouched_without_dropout():
     assert torch.equal(torch.cuda.default_generators[0].get_state(), before)
     with pytest.raises(AssertionError, match="splitkv"):
         flash_attention(q[:, :1, :1], k[:, :1], v[:, :1], dropout_p=0.5)
+
+
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype", [
+    (2, 4, 4, 300, 421, 64, False, torch.float16), (1, 4, 2, 513, 513, 128, True, torch.bfloat16),
+    (4, 4, 4, 200, 1000, 32, True, torch.float16), (1, 2, 1, 1000, 130, 128, True, torch.bfloat16),
+])
+def test_dropout_keep_mask_cache_matches_recomputation(B, Hq, Hk, M, N, D, causal, dtype, monkeypatch):
+    """The backward reads the keep decisions the forward stored; with the cache disabled it re-evaluates
+    Philox, as the reference does. Same decisions, hence the same gradients: bit for bit under
+    deterministic mode (separate kernels), and dK / dV bit for bit in any case."""
+    from flagattention_b200 import flash as flash_mod
+    q, k, v, do = make_qkv(B, Hq, Hk, M, N, D, dtype, "BHTD", 1.0, seed=77, requires_grad=True)
+
+    def grads(limit, deterministic):
+        monkeypatch.setattr(flash_mod, "_KEEP_MASK_LIMIT", limit)
+        torch.cuda.manual_seed(4321)
+        torch.use_deterministic_algorithms(deterministic)
+        try:
+            o = flash_attention(q, k, v, causal, dropout_p=0.3)
+            return (o,) + torch.autograd.grad(o, (q, k, v), do)
+        finally:
+            torch.use_deterministic_algorithms(False)
+
+    for deterministic in (True, False):
+        cached = grads(1 << 30, deterministic)
+        recomputed = grads(0, deterministic)
+        assert torch.equal(cached[0], recomputed[0])
+        assert torch.equal(cached[2], recomputed[2]) and torch.equal(cached[3], recomputed[3])
+        if deterministic:
+            assert torch.equal(cached[1], recomputed[1])
+        else:
+            torch.testing.assert_close(cached[1].float(), recomputed[1].float(), atol=2e-2, rtol=2e-2)
+    check_device_status()
