@@ -189,9 +189,14 @@ def time_kernels(cfg, q, k, v, do, iters=5):
     o = torch.empty_like(q)
     lse = torch.empty(B, Hq, M, dtype=torch.float32, device=dev)
     sm_scale = 1.0 / math.sqrt(D)
+    # dropout: the forward caches its keep decisions for the backward, as flash_attention does
+    keep_mask = None
+    if cfg["dropout_p"] > 0 and cfg["mode"] == "fwd+bwd":
+        keep_mask = torch.empty(lib.b200attn_keep_mask_bytes(B, Hq, M, N) // 4, dtype=torch.int32, device=dev)
+    mask_ptr = keep_mask.data_ptr() if keep_mask is not None else None
     fp = _lib.FwdParams(_lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), lse.data_ptr(),
                         B, Hq, Hkv, M, N, D, dt, dt, int(cfg["causal"]), sm_scale, float(cfg["dropout_p"]),
-                        12345, 0, status.data_ptr())
+                        12345, 0, status.data_ptr(), 0, 0, 0, mask_ptr)
 
     def timed(fn):
         fn()
@@ -216,7 +221,7 @@ def time_kernels(cfg, q, k, v, do, iters=5):
                             _lib.tensor4(do), _lib.tensor4(dq), _lib.tensor4(dk), _lib.tensor4(dv),
                             lse.data_ptr(), delta.data_ptr(), ws.data_ptr(), B, Hq, Hkv, M, N, D, dt, dt,
                             int(cfg["causal"]), sm_scale, float(cfg["dropout_p"]), 12345, 0,
-                            status.data_ptr())
+                            status.data_ptr(), 0, 0, 0, mask_ptr)
         # D = 128 and 64: one fused pass makes dK, dV and dQ (plus the zeroing of its fp32 dQ accumulator),
         # followed by the accumulator's conversion; other head dimensions run two separate kernels.
         names = (("bwd_prep_kernels", 1), ("bwd_kernel<kv+dq>", 2), ("dq_convert_kernel", 4)) if D in (64, 128) else \
