@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory from the REFERENCE's own code.
 
-Run in a container that has the reference checkout (read-only) at ``$FLAG_ATTN_REF`` (default
-``/root/reference``): ``python tests/golden/make_golden.py``. It needs no GPU:
+Run where the reference checkout is available (read-only), with ``FLAG_ATTN_REF`` pointing at it:
+``FLAG_ATTN_REF=<checkout> python tests/golden/make_golden.py``. It needs no GPU:
 
 * ``attention_*.npz``: inputs and outputs of the reference's PyTorch attention
   (``flag_attn.testing.flash_attention``, fp32-upcast and native-dtype), and gradients through it.
@@ -29,7 +29,9 @@ from pathlib import Path
 
 os.environ["TRITON_INTERPRET"] = "1"
 os.environ["PYTHONDONTWRITEBYTECODE"] = "1"
-REF = os.environ.get("FLAG_ATTN_REF", "/root/reference")
+REF = os.environ.get("FLAG_ATTN_REF")
+if not REF or not os.path.isdir(os.path.join(REF, "src", "flag_attn")):
+    raise SystemExit("set FLAG_ATTN_REF to a checkout of the reference (the directory that holds src/flag_attn)")
 sys.path.insert(0, os.path.join(REF, "src"))
 
 import numpy as np  # noqa: E402
