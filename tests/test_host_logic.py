@@ -87,3 +87,25 @@ def test_bench_flash_record_rows_have_the_reference_recorder_keys(tmp_path, monk
     assert line.startswith("[INFO] ")
     detail = json.loads(line[len("[INFO] "):])
     assert detail["op_name"] == "flash_attention" and set(detail["result"][0]) == set(bench_flash.ROW_KEYS)
+
+
+def test_tuned_split_count_is_admissible_for_every_kernel_choice():
+    """b200attn_splitkv_num_splits is host arithmetic (the SM count is passed in): at least one split,
+    no CTA without keys, two partials per CTA for head-packed tiles, one split when the plain grid
+    already fills the device."""
+    lib = _lib.load()
+    for B in (1, 2, 8, 64):
+        for Hkv, groups in ((1, 1), (4, 1), (8, 2), (2, 8), (1, 32), (1, 256)):
+            for M in (1, 2, 5, 300):
+                for N in (1, 100, 4096, 70000, 2 ** 19):
+                    s = lib.b200attn_splitkv_num_splits(B, Hkv * groups, Hkv, M, N, 128, 148)
+                    tiles = -(-N // 128)
+                    rows = groups * M
+                    assert s >= 1
+                    packed = groups > 1 and 2 < rows <= 128
+                    ctas = s // 2 if packed and s % 2 == 0 else s
+                    assert 1 <= ctas <= max(1, tiles), (B, Hkv, groups, M, N, s)
+                    per = -(-tiles // ctas)
+                    assert per * (ctas - 1) < tiles, (B, Hkv, groups, M, N, s)
+                    if rows > 128 and B * Hkv * groups * -(-M // 256) >= 0.8 * 148:
+                        assert s == 1
