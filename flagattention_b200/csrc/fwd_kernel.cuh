@@ -5,7 +5,7 @@
 //   warps 0-3  : softmax + epilogue for query tile 0 (thread r <-> row r, TMEM lane r)
 //   warps 4-7  : softmax + epilogue for query tile 1
 //   warp 8     : tcgen05.mma issuer (one elected lane)
-//   warp 9     : TMA producer (one elected lane); warps 10-11 idle (they complete the third
+//   warp 9     : TMA producer (one elected lane; warp 10 takes the V ring of a paged cache); warps 10-11 otherwise idle (they complete the third
 //                warpgroup so registers can be moved to the softmax groups)
 // TMEM (512 columns): S0 | S1 (128 fp32 columns each, P aliases the first 64 columns of its S
 // as packed 16-bit pairs) and O0 | O1 (D fp32 columns each).
@@ -232,12 +232,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
   };
 
-  if (warp >= 10) {
+  if (warp == 11) {
     reg_dealloc<80>();
-  } else if (warp == 9) {
-    // ------------------------------------------------------------ TMA producer
+  } else if (warp == 9 || warp == 10) {
+    // ------------------------------------------------------------ TMA producers
+    // Warp 9 loads Q and streams the K and V tiles (one elected lane). With a paged cache a tile is
+    // up to 16 small copies per operand and one thread cannot issue them fast enough, so warp 10
+    // then takes the V ring (each ring has its own barriers).
     reg_dealloc<80>();
-    if (lane == 0 && n_max > 0) {
+    if (lane == 0 && n_max > 0 && warp == 9) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
@@ -249,35 +252,51 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           tma_load_4d(sQ + t * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &q_full[t],
                       c * Cfg::CHUNK, packed ? 0 : m0 + t * BLOCK, h, b);
       }
+    }
+    if (lane == 0 && n_max > 0 && !paged && warp == 9) {
+      // Dense K/V: one tile = 128 consecutive keys = one box per 64-column chunk.
       int st = 0;
       uint32_t par = 1;  // first pass over the ring passes at once
       for (int j = 0; j < n_max; ++j, ++st) {
         if (st == stages) { st = 0; par ^= 1; }
         if (!wait(&k_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
-        // One tile = 128 consecutive keys: a single box of the dense tensor, or (paged) as many
-        // boxes as cache blocks the tile spans. Boxes past the sequence's last block re-read that
-        // block, so the tile holds finite numbers everywhere (those keys are masked).
-        auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar) {
-          mbar_expect_tx(bar, Cfg::TILE_BYTES);
-          if (!paged) {
-            for (int c = 0; c < Cfg::NCHUNK; ++c)
-              tma_load_4d(dst + c * Cfg::CHUNK_BYTES, tm, bar, c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
-          } else {
-            const int block = 1 << args.block_shift;
-            const int box_rows = min(block, BLOCK);
-            const int last_blk = (N_ctx - 1) >> args.block_shift;
-            for (int r = 0; r < BLOCK; r += box_rows) {
-              const int n_start = (j0 + j) * BLOCK + r;
-              const int blk = args.block_table[b * args.bt_stride + min(n_start >> args.block_shift, last_blk)];
-              for (int c = 0; c < Cfg::NCHUNK; ++c)
-                tma_load_4d(dst + c * Cfg::CHUNK_BYTES + r * Cfg::ROW_BYTES, tm, bar, c * Cfg::CHUNK,
-                            n_start & (block - 1), hk, blk);
-            }
-          }
-        };
-        load_tile(sK + st * Cfg::TILE_BYTES, &tmK, &k_full[st]);
+        mbar_expect_tx(&k_full[st], Cfg::TILE_BYTES);
+        for (int c = 0; c < Cfg::NCHUNK; ++c)
+          tma_load_4d(sK + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmK, &k_full[st],
+                      c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
         if (!wait(&v_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
-        load_tile(sV + st * Cfg::TILE_BYTES, &tmV, &v_full[st]);
+        mbar_expect_tx(&v_full[st], Cfg::TILE_BYTES);
+        for (int c = 0; c < Cfg::NCHUNK; ++c)
+          tma_load_4d(sV + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmV, &v_full[st],
+                      c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
+      }
+    }
+    if (lane == 0 && n_max > 0 && paged) {
+      // Paged K/V: the tile spans 128 / block cache blocks, one box per block and chunk. Boxes past
+      // the sequence's last block re-read that block, so the tile holds defined data everywhere
+      // (those keys are masked, and stale V rows are cleared before use).
+      const bool k_side = warp == 9;
+      const CUtensorMap* tm = k_side ? &tmK : &tmV;
+      uint8_t* ring = k_side ? sK : sV;
+      uint64_t* full = k_side ? k_full : v_full;
+      uint64_t* empty = k_side ? k_empty : v_empty;
+      const int block = 1 << args.block_shift;
+      const int box_rows = min(block, BLOCK);
+      const int last_blk = (N_ctx - 1) >> args.block_shift;
+      int st = 0;
+      uint32_t par = 1;
+      for (int j = 0; j < n_max; ++j, ++st) {
+        if (st == stages) { st = 0; par ^= 1; }
+        if (!wait(&empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
+        uint8_t* dst = ring + st * Cfg::TILE_BYTES;
+        mbar_expect_tx(&full[st], Cfg::TILE_BYTES);
+        for (int r = 0; r < BLOCK; r += box_rows) {
+          const int n_start = (j0 + j) * BLOCK + r;
+          const int blk = args.block_table[b * args.bt_stride + min(n_start >> args.block_shift, last_blk)];
+          for (int c = 0; c < Cfg::NCHUNK; ++c)
+            tma_load_4d(dst + c * Cfg::CHUNK_BYTES + r * Cfg::ROW_BYTES, tm, &full[st], c * Cfg::CHUNK,
+                        n_start & (block - 1), hk, blk);
+        }
       }
     }
     __syncwarp();
