@@ -517,12 +517,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
 
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      // three-input max: half the instructions of a chain of two-input ones
 #pragma unroll
-      for (int i = 0; i < 128; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
-        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      for (int i = 0; i < 128; i += 8) {
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx0) : "f"(__uint_as_float(s[i + 0])), "f"(__uint_as_float(s[i + 1])));
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx1) : "f"(__uint_as_float(s[i + 2])), "f"(__uint_as_float(s[i + 3])));
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx2) : "f"(__uint_as_float(s[i + 4])), "f"(__uint_as_float(s[i + 5])));
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx3) : "f"(__uint_as_float(s[i + 6])), "f"(__uint_as_float(s[i + 7])));
       }
       const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
 
@@ -553,7 +554,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const float m_eff = (m_run == -INFINITY) ? 0.f : m_run;
       const float neg_ms = -m_eff * qk_scale;
       const uint64_t scale2 = f2_pack(qk_scale, qk_scale), neg_ms2 = f2_pack(neg_ms, neg_ms);
-      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      // scale/shift, row sums and the polynomial run on packed f32x2 instructions (two scores each)
+      uint64_t sum01 = 0ull, sum23 = 0ull;
       // P goes back to TMEM in two halves of 64 keys so that the P V product can start on the
       // first half while the second is still being exponentiated.
 #pragma unroll
@@ -561,22 +563,26 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
         for (int i = half * 64; i < half * 64 + 64; i += 4) {
           float p0, p1, p2, p3;
-          // A fixed subset of the column pairs takes the polynomial route (see PolyMask).
+          const uint64_t x01 = f2_fma(f2_pack(__uint_as_float(s[i + 0]), __uint_as_float(s[i + 1])), scale2, neg_ms2);
+          const uint64_t x23 = f2_fma(f2_pack(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), scale2, neg_ms2);
           if ((PolyMask<D>::value >> ((i >> 1) & 7)) & 1u) {
-            exp2_poly_pair(f2_fma(f2_pack(__uint_as_float(s[i + 0]), __uint_as_float(s[i + 1])), scale2, neg_ms2),
-                           p0, p1);
+            exp2_poly_pair(x01, p0, p1);
           } else {
-            p0 = fast_exp2(fmaf(__uint_as_float(s[i + 0]), qk_scale, neg_ms));
-            p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_ms));
+            float x0, x1;
+            f2_unpack(x01, x0, x1);
+            p0 = fast_exp2(x0);
+            p1 = fast_exp2(x1);
           }
           if ((PolyMask<D>::value >> (((i >> 1) + 1) & 7)) & 1u) {
-            exp2_poly_pair(f2_fma(f2_pack(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), scale2, neg_ms2),
-                           p2, p3);
+            exp2_poly_pair(x23, p2, p3);
           } else {
-            p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, neg_ms));
-            p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, neg_ms));
+            float x2, x3;
+            f2_unpack(x23, x2, x3);
+            p2 = fast_exp2(x2);
+            p3 = fast_exp2(x3);
           }
-          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          sum01 = f2_add(sum01, f2_pack(p0, p1));
+          sum23 = f2_add(sum23, f2_pack(p2, p3));
           if constexpr (DROPOUT) {
             const uint32_t kb = keep_bits[i >> 5] >> (i & 31);
             if (!(kb & 1u)) p0 = 0.f;
@@ -592,6 +598,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         tc_fence_before();
         mbar_arrive(&p_half[2 * t + half]);
       }
+      float sum0, sum1, sum2, sum3;
+      f2_unpack(sum01, sum0, sum1);
+      f2_unpack(sum23, sum2, sum3);
       l_run += (sum0 + sum1) + (sum2 + sum3);
     }
 
