@@ -7,4 +7,4 @@ from .piecewise import piecewise_attention  # noqa: F401
 __all__ = ["flash_attention", "flash_attention_split_kv", "paged_attention", "piecewise_attention",
            "FlashAttentionFunction",
            "check_device_status"]
-__version__ = "0.1.0"
+__version__ = "0.2.0"
