@@ -165,9 +165,12 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise TypeError(f"unsupported dtype {dtype}") from None
 
 
+_Stride4 = c_int64 * 4
+
+
 def tensor4(t: torch.Tensor) -> Tensor4:
-    assert t.dim() == 4
-    return Tensor4(t.data_ptr(), (c_int64 * 4)(*t.stride()))
+    s0, s1, s2, s3 = t.stride()  # raises unless t has four dimensions
+    return Tensor4(t.data_ptr(), _Stride4(s0, s1, s2, s3))
 
 
 def check(rc: int, what: str) -> None:
@@ -177,4 +180,8 @@ def check(rc: int, what: str) -> None:
 
 
 def current_stream_ptr(device: torch.device) -> int:
+    """Raw ``cudaStream_t`` of torch's current stream on ``device``."""
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None and device.index is not None:
+        return raw(device.index)
     return torch.cuda.current_stream(device).cuda_stream

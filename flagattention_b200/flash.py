@@ -48,14 +48,14 @@ def _tma_ready(x: torch.Tensor) -> torch.Tensor:
     """Returns ``x`` or a contiguous copy that satisfies what TMA needs: unit feature stride,
     16-byte aligned base and strides. The reference only copies when the feature stride is not 1
     (``flash.py:28-31``); the extra cases cannot be expressed as a tensor map."""
-    esize = x.element_size()
-    ok = x.stride(-1) == 1 and x.data_ptr() % 16 == 0
+    strides = x.stride()
+    ok = strides[-1] == 1 and x.data_ptr() % 16 == 0
     if ok:
-        for dim in range(3):
-            if x.size(dim) > 1 and (x.stride(dim) * esize) % 16 != 0:
+        esize = x.element_size()
+        for size, stride in zip(x.shape[:-1], strides[:-1]):
+            if size > 1 and (stride <= 0 or (stride * esize) % 16 != 0):
                 ok = False
-            if x.size(dim) > 1 and x.stride(dim) <= 0:
-                ok = False
+                break
     return x if ok else x.contiguous()
 
 
@@ -64,6 +64,7 @@ def _vec_ready(x: torch.Tensor) -> torch.Tensor:
 
 
 _SM_COUNT = {}
+_SPLIT_COUNTS = {}  # (B, H, Hk, M, N, D, SMs) -> tuned split count (a pure function of the key)
 
 
 def _sm_count(device: torch.device) -> int:
@@ -79,7 +80,12 @@ def _split_kv_forward(lib, q, k, v, causal, sm_scale, num_sms, stream, status):
     B, H, M, D = q.shape
     Hk, N = k.shape[1], k.shape[2]
     device = q.device
-    S = int(lib.b200attn_splitkv_num_splits(B, H, Hk, M, N, D, num_sms))
+    key = (B, H, Hk, M, N, D, num_sms)
+    S = _SPLIT_COUNTS.get(key)
+    if S is None:
+        if len(_SPLIT_COUNTS) > 4096:
+            _SPLIT_COUNTS.clear()
+        S = _SPLIT_COUNTS[key] = int(lib.b200attn_splitkv_num_splits(B, H, Hk, M, N, D, num_sms))
     o = torch.empty((B, H, M, D), dtype=q.dtype, device=device)
     rows = B * H * M
     if S > 1:
@@ -132,14 +138,14 @@ def flash_attention_split_kv(q, k, v, causal=False, sm_scale=None):
     q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
     lib = _lib.load()
     device = q.device
-    with torch.no_grad():
-        if device.index == torch.cuda.current_device():
+    # (nothing below is recorded by autograd: the result is a fresh tensor filled by the library)
+    if device.index == torch.cuda.current_device():
+        o, _ = _split_kv_forward(lib, q, k, v, bool(causal), float(sm_scale), _sm_count(device),
+                                 _lib.current_stream_ptr(device), _status_word(device))
+    else:
+        with torch.cuda.device(device):
             o, _ = _split_kv_forward(lib, q, k, v, bool(causal), float(sm_scale), _sm_count(device),
                                      _lib.current_stream_ptr(device), _status_word(device))
-        else:
-            with torch.cuda.device(device):
-                o, _ = _split_kv_forward(lib, q, k, v, bool(causal), float(sm_scale), _sm_count(device),
-                                         _lib.current_stream_ptr(device), _status_word(device))
     return o
 
 
