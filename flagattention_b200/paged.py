@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .flash import _sm_count, _status_word
+from .flash import _SPLIT_COUNTS, _sm_count, _status_word, _tma_ready
 
 _SUPPORTED_HEAD_SIZES = (16, 32, 64, 128)
 
@@ -50,31 +50,38 @@ def paged_attention(query, key_cache, value_cache, context_lens, block_tables, a
     assert max_context_len >= 1
     device = query.device
 
-    def ready(x):
-        ok = x.stride(-1) == 1 and x.data_ptr() % 16 == 0 and all(
-            x.size(i) == 1 or (x.stride(i) * x.element_size()) % 16 == 0 for i in range(x.dim() - 1))
-        return x if ok else x.contiguous()
-
-    query, key_cache, value_cache = ready(query), ready(key_cache), ready(value_cache)
-    context_lens = context_lens.to(device=device, dtype=torch.int32).contiguous()
-    block_tables = block_tables.to(device=device, dtype=torch.int32)
-    if block_tables.stride(-1) != 1:
-        block_tables = block_tables.contiguous()
+    query, key_cache, value_cache = _tma_ready(query), _tma_ready(key_cache), _tma_ready(value_cache)
+    if context_lens.dtype != torch.int32 or context_lens.device != device or not context_lens.is_contiguous():
+        context_lens = context_lens.to(device=device, dtype=torch.int32).contiguous()
+    if block_tables.dtype != torch.int32 or block_tables.device != device or block_tables.stride(-1) != 1:
+        block_tables = block_tables.to(device=device, dtype=torch.int32).contiguous()
     lib = _lib.load()
     out = torch.empty((num_seqs, Hq, D), dtype=query.dtype, device=device)
-    with torch.cuda.device(device):
-        S = int(num_splits) if num_splits and num_splits > 0 else int(
-            lib.b200attn_splitkv_num_splits(num_seqs, Hq, Hkv, 1, max_context_len, D, _sm_count(device)))
-        rows = num_seqs * Hq
+    num_sms = _sm_count(device)
+    if num_splits and num_splits > 0:
+        S = int(num_splits)
+    else:
+        key = (num_seqs, Hq, Hkv, 1, max_context_len, D, num_sms)
+        S = _SPLIT_COUNTS.get(key)
+        if S is None:
+            S = _SPLIT_COUNTS[key] = int(lib.b200attn_splitkv_num_splits(num_seqs, Hq, Hkv, 1, max_context_len, D, num_sms))
+    rows = num_seqs * Hq
+
+    def launch():
         buf = torch.empty(rows * (S * D + S + 1), dtype=torch.float32, device=device)
         part_o = buf.data_ptr()
         part_l = part_o + 4 * rows * S * D
         lse = part_l + 4 * rows * S
-        status = _status_word(device)
         p = _lib.PagedParams(
             _as4(query), _lib.tensor4(key_cache), _lib.tensor4(value_cache), _as4(out),
             block_tables.data_ptr(), block_tables.stride(0), context_lens.data_ptr(),
             lse, part_o, part_l, num_seqs, Hq, Hkv, D, block_size, num_blocks, max_context_len, S,
-            _lib.dtype_code(query.dtype), float(attn_scale), status.data_ptr())
+            _lib.dtype_code(query.dtype), float(attn_scale), _status_word(device).data_ptr())
         _lib.check(lib.b200attn_paged_attention(p, _lib.current_stream_ptr(device)), "b200attn_paged_attention")
+
+    if device.index == torch.cuda.current_device():
+        launch()
+    else:
+        with torch.cuda.device(device):
+            launch()
     return out
