@@ -200,6 +200,52 @@ __device__ __forceinline__ BlockCoord decode_block(int id, int BH, int n_z, int 
   out.bh = c * chunk + rem - out.z * width;
   return out;
 }
+// Division of a non-negative 31-bit integer by a divisor fixed on the host: one high multiply and one
+// shift (mul = ceil(2^(31 + ceil(log2 d)) / d)) instead of the ~40-instruction integer division.
+struct FastDiv {
+  uint32_t d, mul, shr;
+  __host__ static FastDiv make(int64_t divisor) {
+    FastDiv f;
+    f.d = divisor < 1 ? 1u : static_cast<uint32_t>(divisor);
+    f.mul = 0;
+    f.shr = 0;
+    if (f.d > 1) {
+      uint32_t lg = 0;
+      while ((1ull << lg) < f.d) ++lg;
+      const uint32_t p = 31 + lg;
+      f.mul = static_cast<uint32_t>(((1ull << p) + f.d - 1) / f.d);
+      f.shr = p - 32;
+    }
+    return f;
+  }
+  __device__ __forceinline__ int div(int n) const {
+    return d == 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shr);
+  }
+};
+// decode_block() with the divisions prepared on the host.
+struct BlockOrder {
+  FastDiv per_chunk, width, tail_width;
+  int chunk, full;  // pairs per chunk, number of full chunks
+  __host__ static BlockOrder make(int64_t BH, int n_z, int chunk) {
+    BlockOrder o;
+    o.chunk = chunk;
+    o.full = static_cast<int>(BH / chunk);
+    o.per_chunk = FastDiv::make(static_cast<int64_t>(chunk) * n_z);
+    o.width = FastDiv::make(chunk);
+    o.tail_width = FastDiv::make(BH - static_cast<int64_t>(o.full) * chunk);
+    return o;
+  }
+  __device__ __forceinline__ BlockCoord decode(int id) const {
+    int c = per_chunk.div(id);
+    const bool tail = c >= full;
+    if (tail) c = full;
+    const int rem = id - c * static_cast<int>(per_chunk.d);
+    BlockCoord out;
+    out.z = tail ? tail_width.div(rem) : width.div(rem);
+    out.bh = c * chunk + rem - out.z * static_cast<int>(tail ? tail_width.d : width.d);
+    return out;
+  }
+};
 // Number of (batch, head) pairs per chunk: all query heads of as many KV heads as fit `budget`
 // bytes of streamed operand per KV head (`bytes_per_kv_head`), at least one KV head.
 __host__ inline int grid_chunk(int groups, int64_t bytes_per_kv_head, bool causal) {

@@ -12,6 +12,12 @@
 // The two tiles ping-pong: while one tile's softmax runs on the CUDA cores the tensor core
 // executes the other tile's GEMMs.
 //
+// The grid may hold fewer CTAs than work items (one CTA per SM): every role then walks the same
+// list of items, the barrier phases and the K/V ring position carry over from one item to the next,
+// and the loads of the next item's Q and first K/V tiles are issued while the current item's last
+// softmax and epilogue still run, so TMEM allocation, barrier set-up, the first load latency and the
+// output stores of one item hide behind the work of its neighbours.
+//
 // Numerics follow the reference kernel (flash.py:442-509): S = QK^T with fp32 accumulation,
 // base-2 online softmax with qk_scale = sm_scale*log2(e), the row sum taken before dropout and
 // before P is rounded to the input type, O normalised once at the end, LSE = m*sm_scale + ln(l).
@@ -45,7 +51,14 @@ struct FwdArgs {
   float* lse;
   int64_t o_stride_b, o_stride_h, o_stride_m, o_stride_split;
   int64_t lse_stride_b, lse_stride_h, lse_stride_split;
-  int n_zblocks, grid_chunk;        // grid order, see decode_block()
+  int n_zblocks, grid_chunk;        // work-item order, see decode_block()
+  BlockOrder order;                 // the same order with its divisions prepared on the host
+  FastDiv div_heads, div_groups, div_splits;  // by the heads of the item grid, groups, num_splits
+  int o_tma;                        // the output goes through shared memory and TMA stores (16-bit O only)
+  int n_items;                      // number of work items; with fewer CTAs than items CTA c of G takes
+                                    // items c, 2G-1-c, 2G+c, 4G-1-c, ... (the items are sorted from long
+                                    // to short, so this back-and-forth order evens out the CTAs' totals).
+                                    // Only the plain mode (no packing, one split, dense K/V) may do so.
   int num_splits, tiles_per_split;  // split-KV: CTA `split` visits K/V tiles [split*tps, (split+1)*tps)
   int pack_heads;                   // > 0: decode-style packing, the CTA's tile 0 holds all `groups`
                                     // query heads of one KV head (rows = head-major, M rows each,
@@ -78,10 +91,12 @@ struct FwdSmem {
   static constexpr int STAGES = D == 128 ? 2 : (D == 64 ? 3 : 4);
   static constexpr int Q_BYTES = 2 * TileCfg<D>::TILE_BYTES;
   static constexpr int KV_BYTES = STAGES * TileCfg<D>::TILE_BYTES;
-  static constexpr int BAR_OFFSET = Q_BYTES + 2 * KV_BYTES;
+  // Output staging for the TMA stores: one [128 x CHUNK] box per query tile.
+  static constexpr int O_STAGE_BYTES = 2 * TileCfg<D>::CHUNK_BYTES;
+  static constexpr int BAR_OFFSET = Q_BYTES + 2 * KV_BYTES + O_STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;  // barriers + alignment slack
   // Dual-stream mode: one Q tile, as deep a ring as fits (at most 8 stages: the barrier block
-  // holds 10 + 4 * stages barriers in 512 bytes).
+  // holds 14 + 4 * stages barriers in 512 bytes).
   static constexpr int MAX_TOTAL = 232448;
   static constexpr int DUAL_STAGES_FIT = (MAX_TOTAL - 1536 - TileCfg<D>::TILE_BYTES) / (2 * TileCfg<D>::TILE_BYTES);
   static constexpr int DUAL_STAGES = DUAL_STAGES_FIT > 8 ? 8 : DUAL_STAGES_FIT;
@@ -115,7 +130,8 @@ struct PolyMask {
 template <int D, bool BF16, bool DROPOUT>
 __global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-           const __grid_constant__ CUtensorMap tmV, const FwdArgs args) {
+           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+           const FwdArgs args) {
   using Cfg = TileCfg<D>;
   using Sm = FwdSmem<D>;
   constexpr int STAGES = Sm::STAGES;
@@ -124,14 +140,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  // Layout: Q tiles | K ring | V ring | barriers. The dual-stream mode keeps one Q tile (both query
-  // tiles hold the same rows) and spends the space on a deeper ring.
+  // Layout: Q tiles | K ring | V ring | output staging | barriers. The dual-stream mode keeps one Q
+  // tile (both query tiles hold the same rows), no output staging (its partial outputs are fp32 and
+  // stored directly) and spends the space on a deeper ring.
   const bool dual = args.pack_heads > 0 && args.dual_stream != 0;
   const int stages = dual ? args.ring_stages : STAGES;
   uint8_t* sQ = smem;
   uint8_t* sK = smem + (dual ? 1 : 2) * Cfg::TILE_BYTES;
   uint8_t* sV = sK + stages * Cfg::TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + stages * Cfg::TILE_BYTES);
+  uint8_t* sO = sV + stages * Cfg::TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sO + (dual ? 0 : Sm::O_STAGE_BYTES));
   uint64_t* q_full = bars;                  // [2]
   uint64_t* k_full = bars + 2;              // [stages]
   uint64_t* k_empty = k_full + stages;      // [stages]
@@ -140,52 +158,69 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   uint64_t* s_full = v_empty + stages;      // [2]
   uint64_t* p_half = s_full + 2;            // [2 tiles][2 halves]
   uint64_t* o_full = p_half + 4;            // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  uint64_t* q_empty = o_full + 2;           // [2]
+  uint64_t* o_sync = q_empty + 2;           // [2] the four warps of a tile meet here around the output staging
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_sync + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const bool packed = args.pack_heads > 0;
   const int grid_heads = packed ? args.Hkv : args.Hq;
-  const BlockCoord bc = decode_block(blockIdx.x, args.B * grid_heads, args.n_zblocks, args.grid_chunk);
-  const int split = bc.z % args.num_splits;
-  const int m_blk = args.n_zblocks / args.num_splits - 1 - bc.z / args.num_splits;  // longest first
-  const int j_split = split * args.tiles_per_split;  // first K/V tile of this CTA's split
-  const int b = bc.bh / grid_heads;
-  const int hk = packed ? bc.bh % grid_heads : (bc.bh % grid_heads) / args.groups;
-  const int h = packed ? hk * args.groups : bc.bh % grid_heads;   // first (or only) query head
-  const int m0 = m_blk * 2 * BLOCK;
   const bool paged = args.block_table != nullptr;
-  const int N_ctx = paged ? args.context_lens[b] : args.N;
-  const int P_SEQ = N_ctx - args.M;
 
-  // First K/V tile the CTA streams: the split's first tile, or the first tile that the band's far
-  // edge lets the CTA's first query row see (the second query tile then meets one fully masked
-  // tile first, which costs one iteration).
-  int j0 = j_split;
-  if (args.causal && args.d_max < BAND_INF) j0 = max(j0, max(0, m0 + P_SEQ - args.d_max + 1) / BLOCK);
-  // Number of K/V tiles each query tile visits.
-  int n_tiles[2];
+  // One work item: 256 query rows of one (batch, head) and, with split K/V, one range of keys.
+  struct Item {
+    int b, hk, h, m0, split, N_ctx, P_SEQ;
+    int j0;          // first K/V tile the CTA streams
+    int n_tiles[2];  // number of K/V tiles each query tile visits
+    int n_max;       // number of K/V tiles the CTA streams
+  };
+  auto get_item = [&](int id) -> Item {
+    Item it;
+    const BlockCoord bc = args.order.decode(id);
+    const int z_row = args.div_splits.div(bc.z);
+    it.split = bc.z - z_row * args.num_splits;
+    const int m_blk = args.div_splits.div(args.n_zblocks) - 1 - z_row;  // longest first
+    const int j_split = it.split * args.tiles_per_split;  // first K/V tile of this item's split
+    it.b = args.div_heads.div(bc.bh);
+    const int head = bc.bh - it.b * grid_heads;
+    it.hk = packed ? head : args.div_groups.div(head);
+    it.h = packed ? it.hk * args.groups : head;   // first (or only) query head
+    it.m0 = m_blk * 2 * BLOCK;
+    it.N_ctx = paged ? args.context_lens[it.b] : args.N;
+    it.P_SEQ = it.N_ctx - args.M;
+    // First K/V tile: the split's first tile, or the first tile that the band's far edge lets the
+    // item's first query row see (the second query tile then meets one fully masked tile first,
+    // which costs one iteration).
+    it.j0 = j_split;
+    if (args.causal && args.d_max < BAND_INF) it.j0 = max(it.j0, max(0, it.m0 + it.P_SEQ - args.d_max + 1) / BLOCK);
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int mt = m0 + t * BLOCK;
-    int hi = N_ctx;
-    if (args.causal && args.d_min > -BAND_INF) hi = min(N_ctx, max(0, P_SEQ + mt + BLOCK - args.d_min));
-    int n_full = mt < args.M ? cdiv(hi, BLOCK) : 0;
-    if (packed) {
-      // one tile holds every row of every head of the group: rows m = 0..M-1
-      const int hi_p = (args.causal && args.d_min > -BAND_INF) ? min(N_ctx, max(0, P_SEQ + args.M - args.d_min)) : N_ctx;
-      n_full = t == 0 ? cdiv(hi_p, BLOCK) : 0;
+    for (int t = 0; t < 2; ++t) {
+      const int mt = it.m0 + t * BLOCK;
+      int hi = it.N_ctx;
+      if (args.causal && args.d_min > -BAND_INF) hi = min(it.N_ctx, max(0, it.P_SEQ + mt + BLOCK - args.d_min));
+      int n_full = mt < args.M ? cdiv(hi, BLOCK) : 0;
+      if (packed) {
+        // one tile holds every row of every head of the group: rows m = 0..M-1
+        const int hi_p = (args.causal && args.d_min > -BAND_INF) ? min(it.N_ctx, max(0, it.P_SEQ + args.M - args.d_min)) : it.N_ctx;
+        n_full = t == 0 ? cdiv(hi_p, BLOCK) : 0;
+      }
+      it.n_tiles[t] = max(0, min(n_full, j_split + args.tiles_per_split) - it.j0);
     }
-    n_tiles[t] = max(0, min(n_full, j_split + args.tiles_per_split) - j0);
-  }
-  if (dual) {
-    const int n = n_tiles[0];
-    n_tiles[0] = (n + 1) / 2;
-    n_tiles[1] = n / 2;
-  }
-  // Number of K/V tiles the CTA streams.
-  const int n_max = dual ? n_tiles[0] + n_tiles[1] : max(n_tiles[0], n_tiles[1]);
+    if (dual) {
+      const int n = it.n_tiles[0];
+      it.n_tiles[0] = (n + 1) / 2;
+      it.n_tiles[1] = n / 2;
+    }
+    it.n_max = dual ? it.n_tiles[0] + it.n_tiles[1] : max(it.n_tiles[0], it.n_tiles[1]);
+    return it;
+  };
+  // Item of this CTA's k-th round (see FwdArgs::n_items); out of range ends the CTA's list.
+  auto item_of_round = [&](int k) -> int {
+    const int G = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+    return k * G + ((k & 1) ? G - 1 - c : c);
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full[0], 1);
@@ -201,6 +236,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       mbar_init(&p_half[2 * t], 128);
       mbar_init(&p_half[2 * t + 1], 128);
       mbar_init(&o_full[t], 1);
+      mbar_init(&q_empty[t], 1);
+      mbar_init(&o_sync[t], 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -240,62 +277,76 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     // up to 16 small copies per operand and one thread cannot issue them fast enough, so warp 10
     // then takes the V ring (each ring has its own barriers).
     reg_dealloc<80>();
-    if (lane == 0 && n_max > 0 && warp == 9) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      for (int t = 0; t < (dual ? 1 : 2); ++t) {
-        if (n_tiles[t] == 0) continue;
-        // packed: the box is [groups heads x M rows x CHUNK], landing head-major in the tile
-        mbar_expect_tx(&q_full[t], packed ? args.groups * args.M * D * 2 : Cfg::TILE_BYTES);
-        for (int c = 0; c < Cfg::NCHUNK; ++c)
-          tma_load_4d(sQ + t * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &q_full[t],
-                      c * Cfg::CHUNK, packed ? 0 : m0 + t * BLOCK, h, b);
+    if (lane == 0 && (warp == 9 || paged)) {
+      if (warp == 9) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
       }
-    }
-    if (lane == 0 && n_max > 0 && !paged && warp == 9) {
-      // Dense K/V: one tile = 128 consecutive keys = one box per 64-column chunk.
+      // Ring position and barrier phases run on from one work item to the next.
       int st = 0;
-      uint32_t par = 1;  // first pass over the ring passes at once
-      for (int j = 0; j < n_max; ++j, ++st) {
-        if (st == stages) { st = 0; par ^= 1; }
-        if (!wait(&k_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
-        mbar_expect_tx(&k_full[st], Cfg::TILE_BYTES);
-        for (int c = 0; c < Cfg::NCHUNK; ++c)
-          tma_load_4d(sK + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmK, &k_full[st],
-                      c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
-        if (!wait(&v_empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
-        mbar_expect_tx(&v_full[st], Cfg::TILE_BYTES);
-        for (int c = 0; c < Cfg::NCHUNK; ++c)
-          tma_load_4d(sV + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmV, &v_full[st],
-                      c * Cfg::CHUNK, (j0 + j) * BLOCK, hk, b);
-      }
-    }
-    if (lane == 0 && n_max > 0 && paged) {
-      // Paged K/V: the tile spans 128 / block cache blocks, one box per block and chunk. Boxes past
-      // the sequence's last block re-read that block, so the tile holds defined data everywhere
-      // (those keys are masked, and stale V rows are cleared before use).
-      const bool k_side = warp == 9;
-      const CUtensorMap* tm = k_side ? &tmK : &tmV;
-      uint8_t* ring = k_side ? sK : sV;
-      uint64_t* full = k_side ? k_full : v_full;
-      uint64_t* empty = k_side ? k_empty : v_empty;
-      const int block = 1 << args.block_shift;
-      const int box_rows = min(block, BLOCK);
-      const int last_blk = (N_ctx - 1) >> args.block_shift;
-      int st = 0;
-      uint32_t par = 1;
-      for (int j = 0; j < n_max; ++j, ++st) {
-        if (st == stages) { st = 0; par ^= 1; }
-        if (!wait(&empty[st], par)) { fail(ST_WAIT_EMPTY); break; }
-        uint8_t* dst = ring + st * Cfg::TILE_BYTES;
-        mbar_expect_tx(&full[st], Cfg::TILE_BYTES);
-        for (int r = 0; r < BLOCK; r += box_rows) {
-          const int n_start = (j0 + j) * BLOCK + r;
-          const int blk = args.block_table[b * args.bt_stride + min(n_start >> args.block_shift, last_blk)];
-          for (int c = 0; c < Cfg::NCHUNK; ++c)
-            tma_load_4d(dst + c * Cfg::CHUNK_BYTES + r * Cfg::ROW_BYTES, tm, &full[st], c * Cfg::CHUNK,
-                        n_start & (block - 1), hk, blk);
+      uint32_t par = 1;            // first pass over the ring passes at once
+      uint32_t q_par[2] = {1, 1};  // and so does the first use of each Q tile
+      bool alive = true;
+      for (int k = 0; alive; ++k) {
+        const int id = item_of_round(k);
+        if (id >= args.n_items || (k > 0 && *abort_flag)) break;
+        const Item it = get_item(id);
+        if (it.n_max == 0) continue;
+        if (warp == 9) {
+          for (int t = 0; t < (dual ? 1 : 2); ++t) {
+            if (it.n_tiles[t] == 0) continue;
+            // the previous item's last Q K^T on this tile has read the buffer
+            if (!wait(&q_empty[t], q_par[t])) { fail(ST_WAIT_EMPTY); alive = false; break; }
+            q_par[t] ^= 1;
+            // packed: the box is [groups heads x M rows x CHUNK], landing head-major in the tile
+            mbar_expect_tx(&q_full[t], packed ? args.groups * args.M * D * 2 : Cfg::TILE_BYTES);
+            for (int c = 0; c < Cfg::NCHUNK; ++c)
+              tma_load_4d(sQ + t * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &q_full[t],
+                          c * Cfg::CHUNK, packed ? 0 : it.m0 + t * BLOCK, it.h, it.b);
+          }
+          if (!alive) break;
+        }
+        if (!paged) {
+          // Dense K/V: one tile = 128 consecutive keys = one box per 64-column chunk.
+          for (int j = 0; j < it.n_max; ++j, ++st) {
+            if (st == stages) { st = 0; par ^= 1; }
+            if (!wait(&k_empty[st], par)) { fail(ST_WAIT_EMPTY); alive = false; break; }
+            mbar_expect_tx(&k_full[st], Cfg::TILE_BYTES);
+            for (int c = 0; c < Cfg::NCHUNK; ++c)
+              tma_load_4d(sK + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmK, &k_full[st],
+                          c * Cfg::CHUNK, (it.j0 + j) * BLOCK, it.hk, it.b);
+            if (!wait(&v_empty[st], par)) { fail(ST_WAIT_EMPTY); alive = false; break; }
+            mbar_expect_tx(&v_full[st], Cfg::TILE_BYTES);
+            for (int c = 0; c < Cfg::NCHUNK; ++c)
+              tma_load_4d(sV + st * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmV, &v_full[st],
+                          c * Cfg::CHUNK, (it.j0 + j) * BLOCK, it.hk, it.b);
+          }
+        } else {
+          // Paged K/V: the tile spans 128 / block cache blocks, one box per block and chunk. Boxes past
+          // the sequence's last block re-read that block, so the tile holds defined data everywhere
+          // (those keys are masked, and stale V rows are cleared before use).
+          const bool k_side = warp == 9;
+          const CUtensorMap* tm = k_side ? &tmK : &tmV;
+          uint8_t* ring = k_side ? sK : sV;
+          uint64_t* full = k_side ? k_full : v_full;
+          uint64_t* empty = k_side ? k_empty : v_empty;
+          const int block = 1 << args.block_shift;
+          const int box_rows = min(block, BLOCK);
+          const int last_blk = (it.N_ctx - 1) >> args.block_shift;
+          for (int j = 0; j < it.n_max; ++j, ++st) {
+            if (st == stages) { st = 0; par ^= 1; }
+            if (!wait(&empty[st], par)) { fail(ST_WAIT_EMPTY); alive = false; break; }
+            uint8_t* dst = ring + st * Cfg::TILE_BYTES;
+            mbar_expect_tx(&full[st], Cfg::TILE_BYTES);
+            for (int r = 0; r < BLOCK; r += box_rows) {
+              const int n_start = (it.j0 + j) * BLOCK + r;
+              const int blk = args.block_table[it.b * args.bt_stride + min(n_start >> args.block_shift, last_blk)];
+              for (int c = 0; c < Cfg::NCHUNK; ++c)
+                tma_load_4d(dst + c * Cfg::CHUNK_BYTES + r * Cfg::ROW_BYTES, tm, &full[st], c * Cfg::CHUNK,
+                            n_start & (block - 1), it.hk, blk);
+            }
+          }
         }
       }
     }
@@ -305,126 +356,141 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     // The whole warp runs this loop with warp-uniform values; one elected lane issues each
     // tcgen05 instruction (see mma_ss_w).
     reg_dealloc<80>();
-    if (n_max > 0) {
-      constexpr uint32_t IDESC_QK = make_idesc(BF16, 128, BLOCK, false, false);
-      constexpr uint32_t IDESC_PV = make_idesc(BF16, 128, D, false, true);
-      const uint32_t q_addr = smem_u32(sQ);
-      const uint32_t k_addr = smem_u32(sK);
-      const uint32_t v_addr = smem_u32(sV);
-      auto issue_qk = [&](int t, int st) {
-        const uint64_t dq = smem_desc(Cfg::KMAJOR_DESC, q_addr + (dual ? 0 : t) * Cfg::TILE_BYTES);
-        const uint64_t dk = smem_desc(Cfg::KMAJOR_DESC, k_addr + st * Cfg::TILE_BYTES);
+    constexpr uint32_t IDESC_QK = make_idesc(BF16, 128, BLOCK, false, false);
+    constexpr uint32_t IDESC_PV = make_idesc(BF16, 128, D, false, true);
+    const uint32_t q_addr = smem_u32(sQ);
+    const uint32_t k_addr = smem_u32(sK);
+    const uint32_t v_addr = smem_u32(sV);
+    auto issue_qk = [&](int t, int st) {
+      const uint64_t dq = smem_desc(Cfg::KMAJOR_DESC, q_addr + (dual ? 0 : t) * Cfg::TILE_BYTES);
+      const uint64_t dk = smem_desc(Cfg::KMAJOR_DESC, k_addr + st * Cfg::TILE_BYTES);
 #pragma unroll
-        for (int s = 0; s < D / 16; ++s) {
-          // offsets are multiples of 16 bytes inside shared memory: they add into the 14-bit
-          // address field of the descriptor without carrying out of it
-          const uint32_t off = ((s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
-                                (s % Cfg::STEPS_PER_CHUNK) * 32) >> 4;
-          mma_ss_w(tmem_base + t * BLOCK, dq + off, dk + off, IDESC_QK, s > 0 ? 1u : 0u);
-        }
-      };
-      auto issue_pv = [&](int t, int st, bool acc, int half) {
-        const uint64_t dv = smem_desc(Cfg::MNMAJOR_DESC, v_addr + st * Cfg::TILE_BYTES);
+      for (int s = 0; s < D / 16; ++s) {
+        // offsets are multiples of 16 bytes inside shared memory: they add into the 14-bit
+        // address field of the descriptor without carrying out of it
+        const uint32_t off = ((s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
+                              (s % Cfg::STEPS_PER_CHUNK) * 32) >> 4;
+        mma_ss_w(tmem_base + t * BLOCK, dq + off, dk + off, IDESC_QK, s > 0 ? 1u : 0u);
+      }
+    };
+    auto issue_pv = [&](int t, int st, bool acc, int half) {
+      const uint64_t dv = smem_desc(Cfg::MNMAJOR_DESC, v_addr + st * Cfg::TILE_BYTES);
 #pragma unroll
-        for (int s = half * (BLOCK / 32); s < (half + 1) * (BLOCK / 32); ++s) {
-          mma_ts_w(tmem_base + 2 * BLOCK + t * D, tmem_base + t * BLOCK + s * 8,
-                   dv + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_PV, (acc || s > 0) ? 1u : 0u);
-        }
-      };
-      // Paged caches only: the last block of a sequence holds rows past its context length whose
-      // contents are arbitrary. Their probabilities are exactly zero, but 0 x NaN is NaN in the
-      // product, so those V rows are cleared in shared memory before P V reads them.
-      auto clear_stale_v_rows = [&](int st, int j) {
-        if (!paged) return;
-        const int first_bad = N_ctx - (j0 + j) * BLOCK;
-        if (first_bad >= BLOCK) return;
-        uint8_t* tile = sV + st * Cfg::TILE_BYTES;
-        for (int r = max(first_bad, 0) + lane; r < BLOCK; r += 32) {
-          for (int c = 0; c < Cfg::NCHUNK; ++c) {
-            uint4* row = reinterpret_cast<uint4*>(tile + c * Cfg::CHUNK_BYTES + r * Cfg::ROW_BYTES);
+      for (int s = half * (BLOCK / 32); s < (half + 1) * (BLOCK / 32); ++s) {
+        mma_ts_w(tmem_base + 2 * BLOCK + t * D, tmem_base + t * BLOCK + s * 8,
+                 dv + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_PV, (acc || s > 0) ? 1u : 0u);
+      }
+    };
+    // Paged caches only: the last block of a sequence holds rows past its context length whose
+    // contents are arbitrary. Their probabilities are exactly zero, but 0 x NaN is NaN in the
+    // product, so those V rows are cleared in shared memory before P V reads them.
+    // (first_bad: the first row of the tile in ring slot st that lies past the context length)
+    auto clear_stale_v_rows = [&](int st, int first_bad) {
+      if (!paged) return;
+      if (first_bad >= BLOCK) return;
+      uint8_t* tile = sV + st * Cfg::TILE_BYTES;
+      for (int r = max(first_bad, 0) + lane; r < BLOCK; r += 32) {
+        for (int c = 0; c < Cfg::NCHUNK; ++c) {
+          uint4* row = reinterpret_cast<uint4*>(tile + c * Cfg::CHUNK_BYTES + r * Cfg::ROW_BYTES);
 #pragma unroll
-            for (int k = 0; k < Cfg::ROW_BYTES / 16; ++k) row[k] = make_uint4(0, 0, 0, 0);
-          }
+          for (int k = 0; k < Cfg::ROW_BYTES / 16; ++k) row[k] = make_uint4(0, 0, 0, 0);
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-      };
-      auto wait_all = [&](uint64_t* bar, uint32_t parity, int32_t code) -> bool {
-        const bool w = wait(bar, parity);
-        if (__all_sync(0xffffffffu, w)) return true;
-        fail(code);
-        return false;
-      };
-      bool ok = true;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+    };
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int32_t code) -> bool {
+      const bool w = wait(bar, parity);
+      if (__all_sync(0xffffffffu, w)) return true;
+      fail(code);
+      return false;
+    };
+    // Ring slot and phase of the current K/V tile, and the phases of the per-tile barriers: all of
+    // them run on from one work item to the next.
+    int st = 0;
+    uint32_t ph = 0;
+    uint32_t q_ph[2] = {0, 0}, p_ph[2] = {0, 0};
+    for (int k = 0;; ++k) {
+      const int id = item_of_round(k);
+      if (id >= args.n_items || (k > 0 && *abort_flag)) break;
+      const Item it = get_item(id);
+      if (it.n_max == 0) continue;
+      const int n_max = it.n_max;
       if (dual) {
-        // Two independent chains: K/V tile j belongs to query tile j & 1.
-        if (!wait_all(&q_full[0], 0, ST_WAIT_TMA)) ok = false;
+        // Two independent chains: K/V tile j belongs to query tile j & 1. (One item per CTA in
+        // this mode, so the phases below start from zero.)
+        bool ok = wait_all(&q_full[0], 0, ST_WAIT_TMA);
         for (int t = 0; t < 2 && ok; ++t) {
-          if (n_tiles[t] == 0) continue;
+          if (it.n_tiles[t] == 0) continue;
           if (!wait_all(&k_full[t], 0, ST_WAIT_TMA)) { ok = false; break; }  // stages >= 2
           tc_fence_after();
           issue_qk(t, t);
           tc_commit_w(&s_full[t]);
           tc_commit_w(&k_empty[t]);
         }
-        int st = 0, st2 = 2 % stages;               // ring slots of tiles j and j + 2
-        uint32_t ph = 0, ph2 = stages == 2 ? 1 : 0;  // and the phases of their "full" barriers
+        int sd = 0, sd2 = 2 % stages;                // ring slots of tiles j and j + 2
+        uint32_t pd = 0, pd2 = stages == 2 ? 1 : 0;  // and the phases of their "full" barriers
         for (int j = 0; j < n_max && ok; ++j) {
           const int t = j & 1, jj = j >> 1;
           const bool more = j + 2 < n_max;
-          if (!wait_all(&v_full[st], ph, ST_WAIT_TMA)) break;
-          clear_stale_v_rows(st, j);
+          if (!wait_all(&v_full[sd], pd, ST_WAIT_TMA)) break;
+          clear_stale_v_rows(sd, it.N_ctx - (it.j0 + j) * BLOCK);
           if (more) {
-            if (!wait_all(&k_full[st2], ph2, ST_WAIT_TMA)) break;
+            if (!wait_all(&k_full[sd2], pd2, ST_WAIT_TMA)) break;
           }
           if (!wait_all(&p_half[2 * t], jj & 1, ST_WAIT_SOFTMAX)) break;
           tc_fence_after();
-          issue_pv(t, st, jj > 0, 0);
+          issue_pv(t, sd, jj > 0, 0);
           if (!wait_all(&p_half[2 * t + 1], jj & 1, ST_WAIT_SOFTMAX)) break;
           tc_fence_after();
-          issue_pv(t, st, jj > 0, 1);
+          issue_pv(t, sd, jj > 0, 1);
           if (more) {
-            issue_qk(t, st2);
+            issue_qk(t, sd2);
             tc_commit_w(&s_full[t]);
           } else {
             tc_commit_w(&o_full[t]);
           }
-          tc_commit_w(&v_empty[st]);
-          if (more) tc_commit_w(&k_empty[st2]);
-          if (++st == stages) { st = 0; ph ^= 1; }
-          if (++st2 == stages) { st2 = 0; ph2 ^= 1; }
+          tc_commit_w(&v_empty[sd]);
+          if (more) tc_commit_w(&k_empty[sd2]);
+          if (++sd == stages) { sd = 0; pd ^= 1; }
+          if (++sd2 == stages) { sd2 = 0; pd2 ^= 1; }
         }
-        ok = false;  // skip the shared-tile loop below
+        break;
       }
       // Prologue: S_t = Q_t K_0^T for both tiles.
-      if (ok) ok = wait_all(&k_full[0], 0, ST_WAIT_TMA);
+      bool ok = wait_all(&k_full[st], ph, ST_WAIT_TMA);
       for (int t = 0; t < 2 && ok; ++t) {
-        if (n_tiles[t] == 0) continue;
-        if (!wait_all(&q_full[t], 0, ST_WAIT_TMA)) { ok = false; break; }
+        if (it.n_tiles[t] == 0) continue;
+        if (!wait_all(&q_full[t], q_ph[t], ST_WAIT_TMA)) { ok = false; break; }
+        q_ph[t] ^= 1;
         tc_fence_after();
-        issue_qk(t, 0);
+        issue_qk(t, st);
         tc_commit_w(&s_full[t]);
+        if (it.n_tiles[t] == 1) tc_commit_w(&q_empty[t]);  // the item's last read of Q_t
       }
-      if (ok) tc_commit_w(&k_empty[0]);
+      if (ok) tc_commit_w(&k_empty[st]);
       for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j % STAGES;
-        const int st_next = (j + 1) % STAGES;
-        if (!wait_all(&v_full[st], (j / STAGES) & 1, ST_WAIT_TMA)) break;
-        clear_stale_v_rows(st, j);
+        const bool wrap = st + 1 == STAGES;
+        const int st_next = wrap ? 0 : st + 1;
+        const uint32_t ph_next = wrap ? ph ^ 1u : ph;
+        if (!wait_all(&v_full[st], ph, ST_WAIT_TMA)) { ok = false; break; }
+        clear_stale_v_rows(st, it.N_ctx - (it.j0 + j) * BLOCK);
         if (j + 1 < n_max) {
-          if (!wait_all(&k_full[st_next], ((j + 1) / STAGES) & 1, ST_WAIT_TMA)) break;
+          if (!wait_all(&k_full[st_next], ph_next, ST_WAIT_TMA)) { ok = false; break; }
         }
         for (int t = 0; t < 2; ++t) {
-          if (j >= n_tiles[t]) continue;
-          if (!wait_all(&p_half[2 * t], j & 1, ST_WAIT_SOFTMAX)) { ok = false; break; }
+          if (j >= it.n_tiles[t]) continue;
+          if (!wait_all(&p_half[2 * t], p_ph[t], ST_WAIT_SOFTMAX)) { ok = false; break; }
           tc_fence_after();
           issue_pv(t, st, j > 0, 0);
-          if (!wait_all(&p_half[2 * t + 1], j & 1, ST_WAIT_SOFTMAX)) { ok = false; break; }
+          if (!wait_all(&p_half[2 * t + 1], p_ph[t], ST_WAIT_SOFTMAX)) { ok = false; break; }
+          p_ph[t] ^= 1;
           tc_fence_after();
           issue_pv(t, st, j > 0, 1);
-          if (j + 1 < n_tiles[t]) {
+          if (j + 1 < it.n_tiles[t]) {
             issue_qk(t, st_next);
             tc_commit_w(&s_full[t]);
+            if (j + 2 == it.n_tiles[t]) tc_commit_w(&q_empty[t]);  // the item's last read of Q_t
           } else {
             tc_commit_w(&o_full[t]);
           }
@@ -432,7 +498,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (!ok) break;
         tc_commit_w(&v_empty[st]);
         if (j + 1 < n_max) tc_commit_w(&k_empty[st_next]);
+        st = st_next;
+        ph = ph_next;
       }
+      if (!ok) break;
     }
     __syncwarp();
   } else {
@@ -440,16 +509,35 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     reg_alloc<208>();
     const int t = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + lane_base + t * BLOCK;
+    const uint32_t tmem_o = tmem_base + lane_base + 2 * BLOCK + t * D;
+    const float qk_scale = args.qk_scale;
+    const bool warp_idle = packed && (warp & 3) * 32 >= args.groups * args.M;
+    uint32_t s_par = 0, o_par = 0;  // phases of s_full[t] and o_full[t], running on across work items
+    uint32_t sync_par = 0;          // and of o_sync[t]
+    // Meeting point of the tile's four warps (an mbarrier rather than bar.sync so that the wait is
+    // bounded like every other wait of the kernel).
+    auto tile_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_sync[t]);  // one arrival per warp, ordered after its lanes' writes
+      const bool w = wait(&o_sync[t], sync_par);
+      sync_par ^= 1;
+      return w;
+    };
+    bool ok = true;
+
+    for (int k = 0; ok; ++k) {
+    const int id = item_of_round(k);
+    if (id >= args.n_items || (k > 0 && *abort_flag)) break;
+    const Item it = get_item(id);
+    const int b = it.b, h = it.h, m0 = it.m0, j0 = it.j0, N_ctx = it.N_ctx, P_SEQ = it.P_SEQ, split = it.split;
     // Query row and head of this thread; in packed mode rows are (head, m) pairs, head-major.
     const int h_row = packed ? h + row / args.M : h;
     // (rows without a query, and tile 1 when it is unused, get the out-of-range position M)
     const int m_glob = packed ? ((row < args.groups * args.M && (dual || t == 0)) ? row % args.M : args.M)
                               : m0 + t * BLOCK + row;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tmem_s = tmem_base + lane_base + t * BLOCK;
-    const uint32_t tmem_o = tmem_base + lane_base + 2 * BLOCK + t * D;
-    const int nt = n_tiles[t];
-    const float qk_scale = args.qk_scale;
+    const int nt = it.n_tiles[t];
     // Keys n < lim are visible to this row.
     const int lim = (args.causal && args.d_min > -BAND_INF) ? min(N_ctx, max(0, P_SEQ + m_glob + 1 - args.d_min)) : N_ctx;
     // ... and keys n >= lo (the band's far edge).
@@ -470,8 +558,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
     float m_run = -INFINITY;
     float l_run = 0.f;
-    bool ok = true;
-    const bool warp_idle = packed && (warp & 3) * 32 >= args.groups * args.M;
 
     for (int j = 0; j < nt; ++j) {
       // Dropout decisions of this row for the tile's 128 keys, generated before S is awaited so the
@@ -491,8 +577,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
       }
       {
-        const bool w = wait(&s_full[t], j & 1);
+        const bool w = wait(&s_full[t], s_par);
         if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
+        s_par ^= 1;
       }
       if (warp_idle) {
         // No query row lives in this warp's 32 tile rows: keep the barrier protocol, skip the math
@@ -510,10 +597,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       tmem_wait_ld();
 
       if ((jg + 1) * BLOCK > full_upto || jg * BLOCK < full_from) {
-        const int base = jg * BLOCK;
+        // A band edge crosses the tile: this row sees tile columns [lo_rel, hi_rel). Chunks of 32
+        // columns that every row of the warp sees in full are left alone (on the causal diagonal
+        // that is 1.5 of a warp's 4 chunks on average; the comparisons run on the half-rate integer
+        // pipe, which the softmax already loads with its conversions and maxima).
+        const int hi_rel = lim - jg * BLOCK, lo_rel = lo - jg * BLOCK;
+        const int hi_min = __reduce_min_sync(0xffffffffu, hi_rel);
+        const int lo_max = __reduce_max_sync(0xffffffffu, lo_rel);
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (base + i >= lim || base + i < lo) s[i] = 0xff800000u;  // -inf
+        for (int c = 0; c < 4; ++c) {
+          if (32 * c + 32 > hi_min || 32 * c < lo_max) {
+#pragma unroll
+            for (int i = 32 * c; i < 32 * c + 32; ++i)
+              if (i >= hi_rel || i < lo_rel) s[i] = 0xff800000u;  // -inf
+          }
+        }
       }
 
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
@@ -606,15 +704,77 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
     // ------------------------------------------------------------- epilogue
     if (ok && nt > 0) {
-      const bool w = wait(&o_full[t], 0);
+      const bool w = wait(&o_full[t], o_par);
       if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; }
+      o_par ^= 1;
     }
-    if (ok && m_glob < args.M) {
+    auto store_lse = [&]() {
+      if (ok && m_glob < args.M) {
+        const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
+        const float lse = empty ? -INFINITY : m_run * args.sm_scale + logf(l_run);
+        args.lse[b * args.lse_stride_b + h_row * args.lse_stride_h + split_out * args.lse_stride_split + m_glob] = lse;
+      }
+    };
+    if (args.o_tma) {
+      // 16-bit output: each thread scales its row, the tile's four warps lay one [128 x CHUNK] box
+      // out in shared memory in the swizzled layout of the output tensor map, and one thread stores
+      // the box with TMA (rows past M are clipped by the tensor map). The direct path below writes
+      // 32 rows x 16 bytes per warp instruction, which costs several microseconds per tile.
+      tc_fence_after();
       const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
-      const float lse = empty ? -INFINITY : m_run * args.sm_scale + logf(l_run);
-      args.lse[b * args.lse_stride_b + h_row * args.lse_stride_h + split_out * args.lse_stride_split + m_glob] = lse;
+      float inv = empty ? 0.f : 1.0f / l_run;
+      if constexpr (DROPOUT) inv *= args.drop.inv_keep;
+      const bool tile_live = m0 + t * BLOCK < args.M;  // uniform over the tile's four warps
+      const bool issuer = (warp & 3) == 0 && lane == 0;
+      uint8_t* stage = sO + t * Cfg::CHUNK_BYTES;
+      auto stage_chunk = [&](const int c) {
+          uint32_t o[Cfg::CHUNK];
+          if (nt > 0 && ok) {
+#pragma unroll
+            for (int x = 0; x < Cfg::CHUNK; x += 16) tmem_ld16(tmem_o + c * Cfg::CHUNK + x, o + x);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < Cfg::CHUNK; ++i) o[i] = 0u;
+          }
+          // the previous store from this buffer has been read out of shared memory
+          if (issuer) tma_store_wait_read();
+          if (!tile_sync()) { if (ok) fail(ST_WAIT_SOFTMAX); ok = false; }
+          const uint32_t row_addr = smem_u32(stage) + row * Cfg::ROW_BYTES;
+          const uint32_t swz = (row_addr >> 7) & (Cfg::ROW_BYTES / 16 - 1);  // 16-byte unit XOR of the swizzle
+#pragma unroll
+          for (int u = 0; u < Cfg::ROW_BYTES / 16; ++u) {
+            uint4 v;
+            v.x = pack2<BF16>(empty ? 0.f : __uint_as_float(o[8 * u + 0]) * inv,
+                              empty ? 0.f : __uint_as_float(o[8 * u + 1]) * inv);
+            v.y = pack2<BF16>(empty ? 0.f : __uint_as_float(o[8 * u + 2]) * inv,
+                              empty ? 0.f : __uint_as_float(o[8 * u + 3]) * inv);
+            v.z = pack2<BF16>(empty ? 0.f : __uint_as_float(o[8 * u + 4]) * inv,
+                              empty ? 0.f : __uint_as_float(o[8 * u + 5]) * inv);
+            v.w = pack2<BF16>(empty ? 0.f : __uint_as_float(o[8 * u + 6]) * inv,
+                              empty ? 0.f : __uint_as_float(o[8 * u + 7]) * inv);
+            const uint32_t dst = row_addr + ((static_cast<uint32_t>(u) ^ swz) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                         : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          if (!tile_sync()) { if (ok) fail(ST_WAIT_SOFTMAX); ok = false; }
+          if (issuer && ok) {
+            tma_store_4d(&tmO, stage, c * Cfg::CHUNK, m0 + t * BLOCK, h, b);
+            tma_store_commit();
+          }
+      };
+      // The second chunk has to wait until the first has been read out of the staging buffer; the
+      // log-normaliser fills some of that time.
+      if (tile_live) stage_chunk(0);
+      store_lse();
+      if constexpr (Cfg::NCHUNK > 1) {
+        if (tile_live) stage_chunk(1);
+      }
+    } else {
+      store_lse();
     }
-    if (ok) {
+    if (!args.o_tma && ok) {
       tc_fence_after();
       const bool valid = m_glob < args.M;
       const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
@@ -663,7 +823,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           }
         }
       }
+      // The loads of O above have completed (tcgen05.wait::ld) before this thread's next arrival on
+      // p_half, which the MMA warp awaits before the next item's first P V overwrites O.
     }
+    }  // work items
+    // Shared memory must outlive the reads of the last output stores.
+    if (args.o_tma && (warp & 3) == 0 && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();

@@ -6,7 +6,7 @@
 namespace b200attn {
 
 struct FwdLaunch {
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmO;  // tmO only when args.o_tma
   FwdArgs args;
   dim3 grid;
   bool bf16, dropout;
@@ -25,7 +25,7 @@ int launch_fwd_variant(const FwdLaunch& L) {
     B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
-  kernel<<<L.grid, 384, smem, L.stream>>>(L.tmQ, L.tmK, L.tmV, L.args);
+  kernel<<<L.grid, 384, smem, L.stream>>>(L.tmQ, L.tmK, L.tmV, L.tmO, L.args);
   B200ATTN_CUDA_OK(cudaGetLastError());
   return B200ATTN_OK;
 }
