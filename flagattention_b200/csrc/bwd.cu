@@ -138,6 +138,12 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
   kv.args.out1_sb = p->dk.stride[0]; kv.args.out1_sh = p->dk.stride[1]; kv.args.out1_sr = p->dk.stride[2];
   kv.args.out2 = p->dv.ptr;
   kv.args.out2_sb = p->dv.stride[0]; kv.args.out2_sh = p->dv.stride[1]; kv.args.out2_sr = p->dv.stride[2];
+  // Results leave through TMA stores when the output tensors can be described by tensor maps.
+  kv.tmO1 = kv.tmA1; kv.tmO2 = kv.tmA1;
+  kv.args.out_tma = (encode_tmap_4d(&kv.tmO1, p->dk, 2, p->B, p->Hkv, p->N, D, TileCfg<D>::CHUNK, 128,
+                                    TileCfg<D>::TMA_SWZ, "dk") == B200ATTN_OK &&
+                     encode_tmap_4d(&kv.tmO2, p->dv, 2, p->B, p->Hkv, p->N, D, TileCfg<D>::CHUNK, 128,
+                                    TileCfg<D>::TMA_SWZ, "dv") == B200ATTN_OK) ? 1 : 0;
   kv.args.n_zblocks = cdiv(p->N, 128);
   kv.args.grid_chunk = grid_chunk(1, 4ll * a.groups * p->M * D, a.causal != 0);
   kv.grid = dim3(static_cast<unsigned>(static_cast<int64_t>(p->B) * p->Hkv * kv.args.n_zblocks));
@@ -150,6 +156,9 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
   qq.args.out1 = p->dq.ptr;
   qq.args.out1_sb = p->dq.stride[0]; qq.args.out1_sh = p->dq.stride[1]; qq.args.out1_sr = p->dq.stride[2];
   qq.args.out2 = nullptr;
+  qq.tmO1 = qq.tmA1; qq.tmO2 = qq.tmA1;
+  qq.args.out_tma = encode_tmap_4d(&qq.tmO1, p->dq, 2, p->B, p->Hq, p->M, D, TileCfg<D>::CHUNK, 128,
+                                   TileCfg<D>::TMA_SWZ, "dq") == B200ATTN_OK ? 1 : 0;
   qq.args.n_zblocks = cdiv(p->M, 128);
   qq.args.grid_chunk = grid_chunk(a.groups, 4ll * p->N * D, a.causal != 0);
   qq.grid = dim3(static_cast<unsigned>(static_cast<int64_t>(p->B) * p->Hq * qq.args.n_zblocks));
@@ -198,6 +207,8 @@ static int run_total(const b200attn_total_params* p, float2* stats, cudaStream_t
   if ((rc = encode_pair<D>(nullptr, &L.tmB1, p->q, p->B, p->Hq, p->M, "q"))) return rc;
   L.tmA2 = L.tmA1;
   L.tmB2 = L.tmB1;
+  L.tmO1 = L.tmA1;
+  L.tmO2 = L.tmA1;
   BwdArgs a{};
   a.stats = stats;
   a.tot = p->tot;

@@ -68,6 +68,7 @@ struct BwdArgs {
   DropoutCtx drop;
   int32_t* status;
   float* dq_acc;        // FUSED: [B, Hq, M, D] fp32, zero before the launch
+  int out_tma;          // the 16-bit results leave through shared memory and TMA stores (tmO1, tmO2)
 #ifdef B200ATTN_TIMING
   long long* trace;
 #endif
@@ -95,6 +96,7 @@ template <int D, bool BF16, bool DROPOUT, int MODE, bool FUSED = false>
 __global__ void __launch_bounds__((BwdSmem<D, MODE, FUSED>::THREADS), 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
            const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
+           const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
            const BwdArgs args) {
   using Cfg = TileCfg<D>;
   using Sm = BwdSmem<D, MODE, FUSED>;
@@ -135,7 +137,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
   uint64_t* acc_full = p_ready + 2;        // [1]
   uint64_t* dq_ready = acc_full + 1;       // [2] FUSED: dQ^T of the step is complete in TMEM
   uint64_t* dq_drained = dq_ready + 2;     // [2] FUSED: ... and has been read back
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_drained + 2);
+  uint64_t* epi_sync = dq_drained + 2;     // [1] the eight softmax warps meet here before the output stores
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_sync + 1);
   uint8_t* sDS = smem + Sm::DS_OFFSET;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -187,6 +190,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       mbar_init(&dq_drained[i], 128);
     }
     mbar_init(acc_full, 1);
+    mbar_init(epi_sync, 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -630,6 +634,68 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (wg == 0 && ok && row < args.N)
         args.tot[(static_cast<int64_t>(b) * args.Hq + h_first) * args.N + row] = tot_sum + red[row_local];
+    } else if (args.out_tma) {
+      // Each thread scales and rounds its half row of every accumulator into the (now dead) resident
+      // tile of the same index, in the swizzled layout of the output tensor map; one thread then
+      // stores the 128 x D tiles with TMA, which clips rows past the end of the tensor. (Storing from
+      // registers, below, writes 32 rows x 16 bytes per warp instruction and takes several
+      // microseconds per CTA.) Warps that gave up still come to the meeting point.
+      tc_fence_after();
+      const int out_head = MODE == MODE_Q ? h_first : hk;
+      constexpr int NC = D / 2;  // columns per thread and accumulator
+#pragma unroll
+      for (int acc = 0; acc < N_ACC; ++acc) {
+        float scale = args.sm_scale;
+        if (MODE == MODE_KV && acc == 1) scale = DROPOUT ? args.drop.inv_keep : 1.0f;
+        uint32_t o[NC];
+        if (T > 0 && ok) {
+#pragma unroll
+          for (int x = 0; x < NC; x += 8) {
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                : "=r"(o[x + 0]), "=r"(o[x + 1]), "=r"(o[x + 2]), "=r"(o[x + 3]), "=r"(o[x + 4]), "=r"(o[x + 5]),
+                  "=r"(o[x + 6]), "=r"(o[x + 7])
+                : "r"(tmem_base + lane_base + acc * D + wg * NC + x)
+                : "memory");
+          }
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < NC; ++i) o[i] = 0u;
+        }
+        const uint32_t tile = smem_u32(sA + acc * Cfg::TILE_BYTES);
+#pragma unroll
+        for (int x = 0; x < NC; x += 8) {
+          const int c = wg * NC + x;  // first of 8 columns = one 16-byte unit
+          const uint32_t row_addr = tile + (c / Cfg::CHUNK) * Cfg::CHUNK_BYTES + row_local * Cfg::ROW_BYTES;
+          const uint32_t swz = (row_addr >> 7) & (Cfg::ROW_BYTES / 16 - 1);
+          const uint32_t dst = row_addr + (((static_cast<uint32_t>(c % Cfg::CHUNK) >> 3) ^ swz) << 4);
+          const uint32_t v0 = pack2<BF16>(__uint_as_float(o[x + 0]) * scale, __uint_as_float(o[x + 1]) * scale);
+          const uint32_t v1 = pack2<BF16>(__uint_as_float(o[x + 2]) * scale, __uint_as_float(o[x + 3]) * scale);
+          const uint32_t v2 = pack2<BF16>(__uint_as_float(o[x + 4]) * scale, __uint_as_float(o[x + 5]) * scale);
+          const uint32_t v3 = pack2<BF16>(__uint_as_float(o[x + 6]) * scale, __uint_as_float(o[x + 7]) * scale);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                       : "memory");
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(epi_sync);
+      if (warp == 0) {
+        const bool w = wait(epi_sync, 0);
+        if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_SOFTMAX); ok = false; }
+        if (ok && lane == 0 && !*abort_flag) {
+#pragma unroll
+          for (int acc = 0; acc < N_ACC; ++acc) {
+#pragma unroll
+            for (int ch = 0; ch < Cfg::NCHUNK; ++ch)
+              tma_store_4d(acc == 0 ? &tmO1 : &tmO2, sA + acc * Cfg::TILE_BYTES + ch * Cfg::CHUNK_BYTES,
+                           ch * Cfg::CHUNK, r0, out_head, b);
+          }
+          tma_store_commit();
+          tma_store_wait_all();  // shared memory must outlive the reads of the stores
+        }
+      }
     } else if (ok) {
       tc_fence_after();
       const int n_rows = MODE == MODE_Q ? args.M : args.N;

@@ -7,6 +7,7 @@ namespace b200attn {
 
 struct BwdLaunch {
   CUtensorMap tmA1, tmA2, tmB1, tmB2;
+  CUtensorMap tmO1, tmO2;  // outputs, when args.out_tma
   BwdArgs args;
   dim3 grid;
   bool bf16, dropout;
@@ -26,7 +27,7 @@ int launch_bwd_variant(const BwdLaunch& L) {
     B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
-  kernel<<<L.grid, BwdSmem<D, MODE, FUSED>::THREADS, smem, L.stream>>>(L.tmA1, L.tmA2, L.tmB1, L.tmB2, L.args);
+  kernel<<<L.grid, BwdSmem<D, MODE, FUSED>::THREADS, smem, L.stream>>>(L.tmA1, L.tmA2, L.tmB1, L.tmB2, L.tmO1, L.tmO2, L.args);
   B200ATTN_CUDA_OK(cudaGetLastError());
   return B200ATTN_OK;
 }
