@@ -1,12 +1,13 @@
 // Forward attention kernel for sm_100a.
 //
-// One CTA owns 256 query rows of one (batch, head): two 128-row tiles that share every
-// K/V tile brought into shared memory. Roles:
+// A work item is 256 query rows of one (batch, head): two 128-row tiles that share every
+// K/V tile brought into shared memory. Roles of a CTA:
 //   warps 0-3  : softmax + epilogue for query tile 0 (thread r <-> row r, TMEM lane r)
 //   warps 4-7  : softmax + epilogue for query tile 1
 //   warp 8     : tcgen05.mma issuer (one elected lane)
-//   warp 9     : TMA producer (one elected lane; warp 10 takes the V ring of a paged cache); warps 10-11 otherwise idle (they complete the third
-//                warpgroup so registers can be moved to the softmax groups)
+//   warp 9     : TMA producer (one elected lane); warp 10 takes the V ring of a paged cache;
+//                warps 10-11 are otherwise idle (they complete the third warpgroup so that
+//                registers can be moved to the softmax groups)
 // TMEM (512 columns): S0 | S1 (128 fp32 columns each, P aliases the first 64 columns of its S
 // as packed 16-bit pairs) and O0 | O1 (D fp32 columns each).
 // The two tiles ping-pong: while one tile's softmax runs on the CUDA cores the tensor core
