@@ -8,7 +8,7 @@ import torch
 
 from flagattention_b200 import (check_device_status, flash_attention, flash_attention_split_kv, paged_attention,
                                 piecewise_attention)
-from gpu_util import assert_2x_rule, attention_forward, device
+from gpu_util import assert_2x_rule, attention_forward, device, kernel_dropout_mask
 from oracle.paged import paged_attention as oracle_paged
 from oracle.piecewise import piecewise_attention as oracle_piecewise
 
@@ -42,6 +42,43 @@ def test_flash_attention_random(seed):
     o_ref = attention_forward(q, k, v, causal, upcast=True)
     g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
     o_low = attention_forward(q, k, v, causal, upcast=False)
+    g_low = torch.autograd.grad(o_low, (q, k, v), do)
+    check_device_status()
+    assert_2x_rule("o", o, o_low, o_ref)
+    for name, a, b_, c in zip(("dq", "dk", "dv"), grads, g_low, g_ref):
+        assert_2x_rule(name, a, b_, c)
+
+
+@pytest.mark.parametrize("seed", range(200, 212))
+def test_flash_attention_random_many_items(seed):
+    """Shapes with a few hundred 256-row work items (more than the GPU has SMs), so forward CTAs walk
+    several items each; grouped heads, both layouts, causal or not, dropout in a quarter of the cases."""
+    rnd, g, D, dtype = _setup(seed)
+    Hk, G = rnd.choice([2, 4, 8, 12]), rnd.choice([1, 2, 4])
+    Hq = Hk * G
+    M, N, causal = rnd.randint(200, 1500), rnd.randint(1, 3000), rnd.random() < 0.6
+    B = max(2, min(12, (300 * 256) // (Hq * M) + 1))
+    while B > 1 and B * Hq * M * N * 4 > 4e9:
+        B -= 1
+    p = rnd.choice([0.0, 0.0, 0.0, 0.25])
+    transposed = rnd.random() < 0.5
+
+    def mk(H, T):
+        t = _randn(g, dtype, B, T, H, D).transpose(1, 2) if transposed else _randn(g, dtype, B, H, T, D)
+        return t.requires_grad_(True)
+
+    q, k, v = mk(Hq, M), mk(Hk, N), mk(Hk, N)
+    do = _randn(g, dtype, B, Hq, M, D)
+    kw = {}
+    if p > 0:
+        o, _, _, rng_seed, rng_offset = flash_attention(q, k, v, causal, dropout_p=p, return_seed_offset=True)
+        kw = dict(dropout_p=p, dropout_mask=kernel_dropout_mask(B, Hq, M, N, p, int(rng_seed), int(rng_offset)))
+    else:
+        o = flash_attention(q, k, v, causal)
+    grads = torch.autograd.grad(o, (q, k, v), do)
+    o_ref = attention_forward(q, k, v, causal, upcast=True, **kw)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
+    o_low = attention_forward(q, k, v, causal, upcast=False, **kw)
     g_low = torch.autograd.grad(o_low, (q, k, v), do)
     check_device_status()
     assert_2x_rule("o", o, o_low, o_ref)
