@@ -125,6 +125,7 @@ SYMBOLS = {
     "b200attn_abi_version": (c_int32, []),
     "b200attn_last_error": (c_char_p, []),
     "b200attn_umma_selftest": (c_int32, [POINTER(SelftestParams), c_void_p]),
+    "b200attn_work_order_selftest": (c_int32, [c_int32, c_int32, c_int32]),
 }
 
 _LIB = None

@@ -218,8 +218,12 @@ struct FastDiv {
     }
     return f;
   }
-  __device__ __forceinline__ int div(int n) const {
+  __host__ __device__ __forceinline__ int div(int n) const {
+#ifdef __CUDA_ARCH__
     return d == 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shr);
+#else
+    return d == 1 ? n : static_cast<int>(static_cast<uint32_t>((static_cast<uint64_t>(static_cast<uint32_t>(n)) * mul) >> 32) >> shr);
+#endif
   }
 };
 // decode_block() with the divisions prepared on the host.
@@ -235,7 +239,7 @@ struct BlockOrder {
     o.tail_width = FastDiv::make(BH - static_cast<int64_t>(o.full) * chunk);
     return o;
   }
-  __device__ __forceinline__ BlockCoord decode(int id) const {
+  __host__ __device__ __forceinline__ BlockCoord decode(int id) const {
     int c = per_chunk.div(id);
     const bool tail = c >= full;
     if (tail) c = full;

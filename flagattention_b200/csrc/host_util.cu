@@ -129,3 +129,31 @@ extern "C" {
 int b200attn_abi_version(void) { return B200ATTN_ABI_VERSION; }
 const char* b200attn_last_error(void) { return b200attn::last_error(); }
 }
+
+// Host-side check of the prepared divisions behind the kernels' work-item order: every id of a grid
+// of `pairs` (batch, head) pairs x `n_z` row blocks in chunks of `chunk` pairs must decode to the
+// pair and block that plain integer division gives. Returns the number of ids that do not.
+extern "C" int b200attn_work_order_selftest(int32_t pairs, int32_t n_z, int32_t chunk) {
+  using namespace b200attn;
+  if (pairs <= 0 || n_z <= 0 || chunk <= 0 || static_cast<int64_t>(pairs) * n_z > 0x7fffffff) {
+    set_error("work_order_selftest: bad argument");
+    return B200ATTN_EINVAL;
+  }
+  const BlockOrder order = BlockOrder::make(pairs, n_z, chunk);
+  const int per_chunk = chunk * n_z, full = pairs / chunk;
+  int bad = 0;
+  for (int id = 0; id < pairs * n_z; ++id) {
+    int c = id / per_chunk, width = chunk;
+    if (c >= full) { c = full; width = pairs - full * chunk; }
+    const int rem = id - c * per_chunk;
+    const int z = rem / width, bh = c * chunk + rem - z * width;
+    const BlockCoord got = order.decode(id);
+    if (got.z != z || got.bh != bh) ++bad;
+  }
+  const FastDiv by_pairs = FastDiv::make(pairs);
+  for (int64_t n = 0; n < 0x7fffffff; n += 1 + n / 97) {
+    if (by_pairs.div(static_cast<int>(n)) != static_cast<int>(n / pairs)) ++bad;
+  }
+  if (by_pairs.div(0x7fffffff) != 0x7fffffff / pairs) ++bad;
+  return bad;
+}

@@ -263,6 +263,12 @@ typedef struct {
 
 int b200attn_umma_selftest(const b200attn_selftest_params* p, void* stream);
 
+/* Host-only check (no GPU needed) of the prepared divisions with which the kernels turn a work-item
+ * number into (batch, head) pair and row block: `pairs` pairs x `n_z` row blocks, visited in chunks
+ * of `chunk` pairs. Returns the number of item numbers that decode differently from plain integer
+ * division (0 = correct), or a negative code for bad arguments. No counterpart in the reference. */
+int b200attn_work_order_selftest(int32_t pairs, int32_t n_z, int32_t chunk);
+
 #ifdef __cplusplus
 }
 #endif

@@ -109,3 +109,14 @@ def test_tuned_split_count_is_admissible_for_every_kernel_choice():
                     assert per * (ctas - 1) < tiles, (B, Hkv, groups, M, N, s)
                     if rows > 128 and B * Hkv * groups * -(-M // 256) >= 0.8 * 148:
                         assert s == 1
+
+
+def test_prepared_work_item_decode_matches_plain_division():
+    """The kernels turn a work-item number into (batch, head) pair and row block with divisions
+    prepared on the host (one high multiply and a shift each); the library checks them against plain
+    integer division over whole grids, including ragged last chunks and power-of-two sizes."""
+    lib = _lib.load()
+    for pairs, n_z, chunk in [(128, 16, 192), (128, 16, 128), (1024, 2, 48), (37, 5, 7), (1, 1, 1), (64, 128, 48),
+                              (4096, 4, 1), (3, 1000, 2), (255, 17, 256), (2048, 16, 4096)]:
+        assert lib.b200attn_work_order_selftest(pairs, n_z, chunk) == 0, (pairs, n_z, chunk)
+    assert lib.b200attn_work_order_selftest(0, 1, 1) < 0
