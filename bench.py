@@ -259,10 +259,22 @@ def slice_flops(cfg) -> float:
     return step_flops(cfg) / (cfg["B"] * cfg["Hkv"])
 
 
+def use_all_host_threads() -> int:
+    """The CPU legs run on every host core this process may use. (torchrun exports OMP_NUM_THREADS=1
+    to its workers, which would otherwise leave the reference arm of a multi-GPU launch on one core.)"""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    if torch.get_num_threads() != n:
+        torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
 def cpu_baseline(cfg, budget_s=12.0, max_slices=64):
     """Times the oracle (native-dtype path, i.e. the reference's PyTorch CPU attention) on whole
     (batch, KV-group) units until `budget_s` seconds or `max_slices` units have run."""
-    threads = torch.get_num_threads()
+    threads = use_all_host_threads()
     q, k, v, do = cpu_slice_inputs(cfg)
     # long-context slices do not fit the budget: shrink the query rows of the sample and say so
     rows = cfg["M"]
@@ -339,6 +351,7 @@ def main():
         # oracle/), all host threads, one (batch, KV-group) unit of the workload per step.
         if rank != 0:
             return
+        use_all_host_threads()
         q, k, v, do = cpu_slice_inputs(cfg)
         rows = cfg["M"]
         if cfg["M"] * cfg["N"] > 4096 * 4096 * 4:
