@@ -6,11 +6,13 @@ and paged-cache decode (the shapes of ``benchmark/paged_benchmark.py``).
 The operation is a pure stream over K and V, so the figure of merit is the rate at which the K/V
 bytes are consumed, compared with the measured HBM copy bandwidth of the device.
 
-    python -m flagattention_b200.bench_decoding [--json] [--with-torch]
+    python -m flagattention_b200.bench_decoding [--json] [--with-torch] [--graph]
 
 Every timed loop rotates over enough independent K/V copies that the working set exceeds the L2
 cache (126 MB), so the rate is an HBM rate at every N. Timing is by CUDA events on the launching
-stream around ``iters`` back-to-back calls of the public operator, after warm-up.
+stream around ``iters`` back-to-back calls of the public operator, after warm-up. At short contexts
+a call costs more on the host (about 30 us) than on the device; ``--graph`` captures the same calls
+into a CUDA graph and times its replay, which is what a serving loop that replays graphs would see.
 """
 from __future__ import annotations
 
@@ -60,17 +62,35 @@ def _torch_attention(q, k, v):
     return p.to(v.dtype) @ v
 
 
-def run_case(B, Hq, Hk, M, N, D, dtype, iters, with_torch, device):
+def _graph_ms(call, copies, iters):
+    """Device time per call when `copies` calls (one per K/V copy) are replayed from a CUDA graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call(0)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(copies):
+                call(i)
+    torch.cuda.current_stream().wait_stream(side)
+    replays = max(1, iters // copies)
+    return _time_ms(lambda i: graph.replay(), replays, warmup=2) / copies
+
+
+def run_case(B, Hq, Hk, M, N, D, dtype, iters, with_torch, device, graph=False):
     kv_bytes = 2 * B * Hk * N * D * 2
     copies = max(1, min(16, -(-2 * L2_BYTES // kv_bytes)))
     qs = [torch.randn(B, Hq, M, D, device=device, dtype=dtype) for _ in range(copies)]
     ks = [torch.randn(B, Hk, N, D, device=device, dtype=dtype) for _ in range(copies)]
     vs = [torch.randn(B, Hk, N, D, device=device, dtype=dtype) for _ in range(copies)]
-    ms = _time_ms(lambda i: flash_attention_split_kv(qs[i % copies], ks[i % copies], vs[i % copies]), iters)
+    call = lambda i: flash_attention_split_kv(qs[i % copies], ks[i % copies], vs[i % copies])  # noqa: E731
+    ms = _graph_ms(call, copies, iters) if graph else _time_ms(call, iters)
     row = {
         "B": B, "Hq": Hq, "Hkv": Hk, "M": M, "N": N, "D": D, "dtype": str(dtype)[6:],
         "splits": int(_lib.load().b200attn_splitkv_num_splits(B, Hq, Hk, M, N, D, 0)),
         "kv_copies_rotated": copies, "us": round(ms * 1e3, 2), "kv_gbs": round(kv_bytes / ms / 1e6, 1),
+        "timed": "cuda graph replay" if graph else "eager calls",
     }
     if with_torch:
         t_ms = _time_ms(lambda i: _torch_attention(qs[i % copies], ks[i % copies], vs[i % copies]),
@@ -103,6 +123,8 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--json", action="store_true", help="one JSON object per line instead of a table")
     ap.add_argument("--with-torch", action="store_true", help="also time the plain PyTorch formula")
+    ap.add_argument("--graph", action="store_true",
+                    help="time the one-token and grouped-head cases as CUDA graph replays (no host cost per call)")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--min-log2-n", type=int, default=9)
     ap.add_argument("--max-log2-n", type=int, default=19)
@@ -126,7 +148,7 @@ def main():
     for tag, B, Hq, Hk, M, N, D, dtype in cases:
         if args.case and not tag.startswith(args.case):
             continue
-        row = run_case(B, Hq, Hk, M, N, D, dtype, args.iters, args.with_torch, device)
+        row = run_case(B, Hq, Hk, M, N, D, dtype, args.iters, args.with_torch, device, args.graph)
         row.update(case=tag, hbm_peak_gbs=peak, hbm_peak_kind=peak_kind, frac=round(row["kv_gbs"] / peak, 3))
         if args.json:
             print(json.dumps(row), flush=True)
