@@ -122,6 +122,8 @@ SYMBOLS = {
     "b200attn_paged_attention": (c_int32, [POINTER(PagedParams), c_void_p]),
     "b200attn_merge_partial": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "b200attn_merge_partial_store": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                               c_int32, POINTER(Tensor4), c_int32, c_void_p]),
     "b200attn_abi_version": (c_int32, []),
     "b200attn_last_error": (c_char_p, []),
     "b200attn_umma_selftest": (c_int32, [POINTER(SelftestParams), c_void_p]),

@@ -189,6 +189,48 @@ merge_partial_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc, con
   }
 }
 
+// The same merge for two complete partial results [B, H, M, D] whose sum is final: the merged row goes
+// straight to the 16-bit output tensor (its own strides) and only the log-normaliser is updated in
+// place, which saves the fp32 write-back and the separate conversion pass. One thread per 8 features.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+merge_store_kernel(const float* __restrict__ o_a, float* __restrict__ lse_a, const float* __restrict__ o_b,
+                   const float* __restrict__ lse_b, uint16_t* __restrict__ out, int64_t out_sb, int64_t out_sh,
+                   int64_t out_sm, int H, int M, int D, int64_t total) {
+  const int vec_per_row = D / 8;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / vec_per_row;
+    const int vec = static_cast<int>(i - row * vec_per_row);
+    const float la = lse_a[row], lb = lse_b[row];
+    const float mx = fmaxf(la, lb);
+    float wa = 0.f, wb = 0.f, lse = -INFINITY;
+    if (mx != -INFINITY) {
+      const float ea = __expf(la - mx), eb = __expf(lb - mx);
+      const float inv = 1.0f / (ea + eb);
+      wa = ea * inv;
+      wb = eb * inv;
+      lse = mx + __logf(ea + eb);
+    }
+    const float4* pa = reinterpret_cast<const float4*>(o_a + row * D) + 2 * vec;
+    const float4* pb = reinterpret_cast<const float4*>(o_b + row * D) + 2 * vec;
+    const float4 a0 = pa[0], a1 = pa[1], b0 = pb[0], b1 = pb[1];
+    uint4 v;
+    v.x = pack2<BF16>(a0.x * wa + b0.x * wb, a0.y * wa + b0.y * wb);
+    v.y = pack2<BF16>(a0.z * wa + b0.z * wb, a0.w * wa + b0.w * wb);
+    v.z = pack2<BF16>(a1.x * wa + b1.x * wb, a1.y * wa + b1.y * wb);
+    v.w = pack2<BF16>(a1.z * wa + b1.z * wb, a1.w * wa + b1.w * wb);
+    const int64_t bh = row / M;
+    const int m = static_cast<int>(row - bh * M);
+    const int64_t b = bh / H;
+    const int h = static_cast<int>(bh - b * H);
+    *reinterpret_cast<uint4*>(out + b * out_sb + h * out_sh + static_cast<int64_t>(m) * out_sm + 8 * vec) = v;
+    // (the lanes of a row sit in one warp and have all read lse_a[row] above)
+    __syncwarp(__activemask());
+    if (vec == vec_per_row - 1) lse_a[row] = lse;
+  }
+}
+
 static int check_vec_tensor(const b200attn_tensor* t, int eb, const char* name) {
   if (t == nullptr || t->ptr == nullptr) {
     set_error("%s: null tensor", name);
@@ -282,6 +324,42 @@ extern "C" int b200attn_merge_partial(float* o_acc, float* lse_acc, const float*
   merge_partial_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       o_acc, lse_acc, o_part, lse_part, heads, rows, D, acc_rows_per_head, acc_row0, part_rows_per_head,
       part_row0, first ? 1 : 0);
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
+}
+
+
+extern "C" int b200attn_merge_partial_store(const float* o_a, float* lse_a, const float* o_b, const float* lse_b,
+                                            int32_t B, int32_t H, int32_t M, int32_t D, const b200attn_tensor* out,
+                                            int32_t out_dtype, void* stream) {
+  using namespace b200attn;
+  if (o_a == nullptr || lse_a == nullptr || o_b == nullptr || lse_b == nullptr || B <= 0 || H <= 0 || M <= 0 ||
+      (D != 16 && D != 32 && D != 64 && D != 128)) {
+    set_error("merge_partial_store: bad argument");
+    return B200ATTN_EINVAL;
+  }
+  if (out_dtype != B200ATTN_F16 && out_dtype != B200ATTN_BF16) {
+    set_error("merge_partial_store: the output must be fp16 or bf16");
+    return B200ATTN_EINVAL;
+  }
+  if (reinterpret_cast<uintptr_t>(o_a) % 16 != 0 || reinterpret_cast<uintptr_t>(o_b) % 16 != 0) {
+    set_error("merge_partial_store: partial outputs must be 16-byte aligned");
+    return B200ATTN_EINVAL;
+  }
+  const int rc = check_vec_tensor(out, 2, "merge_partial_store.out");
+  if (rc) return rc;
+  const int64_t total = static_cast<int64_t>(B) * H * M * (D / 8);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  uint16_t* dst = static_cast<uint16_t*>(out->ptr);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == B200ATTN_BF16) {
+    merge_store_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        o_a, lse_a, o_b, lse_b, dst, out->stride[0], out->stride[1], out->stride[2], H, M, D, total);
+  } else {
+    merge_store_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+        o_a, lse_a, o_b, lse_b, dst, out->stride[0], out->stride[1], out->stride[2], H, M, D, total);
+  }
   B200ATTN_CUDA_OK(cudaGetLastError());
   return B200ATTN_OK;
 }

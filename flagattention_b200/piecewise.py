@@ -6,7 +6,8 @@ this library's kernels.
 bands of the distance, so the row's softmax is the normaliser-weighted merge of two band-limited
 attentions: the forward runs the forward kernel once per (q, k) pair with the band mask of its region
 (``b200attn_fwd`` with ``band``), writing fp32 partial outputs and log-normalisers, and merges them
-(``b200attn_merge_partial``, the algebra of the split-KV combine). The backward runs the backward
+(``b200attn_merge_partial_store``, the algebra of the split-KV combine, rounding straight into the
+output). The backward runs the backward
 kernels once per pair with the same bands, both on the merged log-normaliser and on ``delta`` of the
 merged output; each call yields its pair's dQ and dK, and the two dV contributions are added.
 """
@@ -64,10 +65,10 @@ class PiecewiseAttentionFunction(torch.autograd.Function):
                 _lib.check(lib.b200attn_fwd(fp, stream), "b200attn_fwd")
                 parts.append((o_part, l_part))
             (o_acc, L), (o_far, l_far) = parts
-            _lib.check(lib.b200attn_merge_partial(o_acc.data_ptr(), L.data_ptr(), o_far.data_ptr(), l_far.data_ptr(),
-                                                  B * H, M, D, M, 0, M, 0, 0, stream), "b200attn_merge_partial")
             o = torch.empty_like(q1)
-            o.copy_(o_acc)
+            _lib.check(lib.b200attn_merge_partial_store(o_acc.data_ptr(), L.data_ptr(), o_far.data_ptr(),
+                                                        l_far.data_ptr(), B, H, M, D, _lib.tensor4(o), dt, stream),
+                       "b200attn_merge_partial_store")
         ctx.save_for_backward(q1, k1, q2, k2, v, o, L)
         ctx.sm_scale = sm_scale
         ctx.causal = bool(causal)

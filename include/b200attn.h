@@ -233,6 +233,14 @@ int b200attn_merge_partial(float* o_acc, float* lse_acc, const float* o_part, co
                            int32_t acc_row0, int32_t part_rows_per_head, int32_t part_row0,
                            int32_t first, void* stream);
 
+/* The same merge for two complete partial results [B, H, M, D] (contiguous fp32, with fp32
+ * log-normalisers [B, H, M]) whose sum is the final result: the merged rows are rounded straight into
+ * the fp16/bf16 tensor `out` (own strides, 16-byte aligned rows) and `lse_a` receives the merged
+ * log-normaliser. Used by piecewise attention's forward (the two regions of `piecewise.py:69-84`). */
+int b200attn_merge_partial_store(const float* o_a, float* lse_a, const float* o_b, const float* lse_b,
+                                 int32_t B, int32_t H, int32_t M, int32_t D, const b200attn_tensor* out,
+                                 int32_t out_dtype, void* stream);
+
 /* Diagnostics. */
 int b200attn_abi_version(void);
 const char* b200attn_last_error(void);

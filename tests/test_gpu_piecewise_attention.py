@@ -154,3 +154,32 @@ def test_band_mask_through_the_c_abi(dmin, dmax, D):
         for name, a, b_, c in zip(("dq", "dk", "dv"), (dq, dk, dv), g_low, g_ref):
             assert_2x_rule(name, a, b_, c)
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("D", [16, 128])
+def test_merge_partial_store_equals_merge_then_round(D, dtype):
+    """The merge that rounds straight into a 16-bit tensor (transposed layout here) gives the bits of
+    the in-place fp32 merge followed by a cast, and the same log-normaliser; rows that one or both
+    partials leave empty (log-normaliser -inf) included."""
+    B, H, M = 2, 3, 77
+    g = torch.Generator(device=device()).manual_seed(5)
+    o_a = torch.randn(B, H, M, D, device=device(), generator=g)
+    o_b = torch.randn(B, H, M, D, device=device(), generator=g)
+    l_a = torch.randn(B, H, M, device=device(), generator=g) * 3
+    l_b = torch.randn(B, H, M, device=device(), generator=g) * 3
+    l_a[0, 0, :5] = float("-inf")
+    l_b[0, 0, 3:9] = float("-inf")
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    ref_o, ref_l = o_a.clone(), l_a.clone()
+    _lib.check(lib.b200attn_merge_partial(ref_o.data_ptr(), ref_l.data_ptr(), o_b.data_ptr(), l_b.data_ptr(),
+                                          B * H, M, D, M, 0, M, 0, 0, st), "merge_partial")
+    out = torch.empty(B, M, H, D, dtype=dtype, device=device()).transpose(1, 2)
+    got_l = l_a.clone()
+    _lib.check(lib.b200attn_merge_partial_store(o_a.data_ptr(), got_l.data_ptr(), o_b.data_ptr(), l_b.data_ptr(),
+                                                B, H, M, D, _lib.tensor4(out), _lib.dtype_code(dtype), st),
+               "merge_partial_store")
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref_o.to(dtype))
+    assert torch.equal(got_l, ref_l)
