@@ -495,15 +495,19 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           if constexpr (MODE == MODE_Q) {
             keep_bits = row < args.M ? mk[static_cast<int64_t>(col0 >> 5) * args.M + row] : 0u;
           } else {
-            // the warp's 32 key rows share one word index; lane c fetches query col0 + c's word, then
-            // every lane picks its own key's bit out of each
+            // the warp's 32 key rows share one word index; lane c fetches query col0 + c's word (bit l =
+            // key l of the warp), and a 32 x 32 bit transpose across the warp (five butterfly steps)
+            // leaves in lane l the word whose bit c is the decision for (key l, query col0 + c)
             const int wi = (r0 + (warp & 3) * 32) >> 5;
-            const uint32_t wq = (col0 + lane < args.M && wi < args.drop.mask_words)
-                                    ? mk[static_cast<int64_t>(wi) * args.M + col0 + lane] : 0u;
-            keep_bits = 0u;
+            keep_bits = (col0 + lane < args.M && wi < args.drop.mask_words)
+                            ? mk[static_cast<int64_t>(wi) * args.M + col0 + lane] : 0u;
 #pragma unroll
-            for (int c = 0; c < 32; ++c)
-              keep_bits |= ((__shfl_sync(0xffffffffu, wq, c) >> lane) & 1u) << c;
+            for (int s = 16; s >= 1; s >>= 1) {
+              const uint32_t m = s == 16 ? 0x0000ffffu : s == 8 ? 0x00ff00ffu : s == 4 ? 0x0f0f0f0fu
+                                 : s == 2 ? 0x33333333u : 0x55555555u;
+              const uint32_t y = __shfl_xor_sync(0xffffffffu, keep_bits, s);
+              keep_bits = (lane & s) ? ((keep_bits & ~m) | ((y >> s) & m)) : ((keep_bits & m) | ((y << s) & ~m));
+            }
           }
         } else if constexpr (MODE == MODE_Q) {
           keep_bits = dropout_keep_word(args.drop, head_base + static_cast<uint64_t>(row) * args.N + col0);
