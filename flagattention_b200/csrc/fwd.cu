@@ -169,27 +169,62 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
 namespace b200attn {
 
 // O[row] = sum_s w_s O_s[row] / sum_s w_s with w_s = exp(lse_s - max_s lse_s);
-// LSE[row] = max + log(sum_s w_s). One block per (b, h, m) row, one thread per feature.
+// LSE[row] = max + log(sum_s w_s). One block of 128 threads per (b, h, m) row. The splits'
+// log-normalisers are read, reduced to their maximum and turned into weights by all threads in
+// parallel (kept in shared memory for the first 1024 splits); then thread d accumulates feature d
+// over the splits with independent, unrolled loads. (Three dependent loops over the splits per thread
+// made this kernel as long as the partial pass itself on decode shapes.)
 template <bool BF16>
-__global__ void splitkv_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                       void* __restrict__ o, float* __restrict__ lse, int64_t o_sb,
-                                       int64_t o_sh, int64_t o_sm, int H, int M, int D, int S) {
+__global__ void __launch_bounds__(128)
+splitkv_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                       void* __restrict__ o, float* __restrict__ lse, int64_t o_sb,
+                       int64_t o_sh, int64_t o_sm, int H, int M, int D, int S) {
+  constexpr int CACHED = 1024;
+  __shared__ float w_sh[CACHED];
+  __shared__ float red[4];
   const int64_t row = blockIdx.x;  // (b*H + h)*M + m
   const int m = static_cast<int>(row % M);
   const int64_t bh = row / M;
   const int h = static_cast<int>(bh % H);
   const int64_t b = bh / H;
   const float* l = part_lse + bh * S * M + m;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  auto block_reduce = [&](float x, bool is_max) -> float {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const float y = __shfl_xor_sync(0xffffffffu, x, off);
+      x = is_max ? fmaxf(x, y) : x + y;
+    }
+    __syncthreads();  // (also orders the writes to w_sh before their readers)
+    if (lane == 0) red[wid] = x;
+    __syncthreads();
+    return is_max ? fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])) : (red[0] + red[1]) + (red[2] + red[3]);
+  };
   float mx = -INFINITY;
-  for (int s = 0; s < S; ++s) mx = fmaxf(mx, l[static_cast<int64_t>(s) * M]);
-  float denom = 0.f;
-  for (int s = 0; s < S; ++s) denom += (mx == -INFINITY) ? 0.f : expf(l[static_cast<int64_t>(s) * M] - mx);
-  const int d = threadIdx.x;
+  for (int s = tid; s < S; s += 128) {
+    const float x = l[static_cast<int64_t>(s) * M];
+    if (s < CACHED) w_sh[s] = x;
+    mx = fmaxf(mx, x);
+  }
+  mx = block_reduce(mx, true);
+  float part = 0.f;
+  for (int s = tid; s < S; s += 128) {
+    const float x = s < CACHED ? w_sh[s] : l[static_cast<int64_t>(s) * M];
+    const float w = (mx == -INFINITY) ? 0.f : expf(x - mx);
+    if (s < CACHED) w_sh[s] = w;
+    part += w;
+  }
+  const float denom = block_reduce(part, false);
+  const int d = tid;
   if (d < D) {
     float acc = 0.f;
+    const float* po = part_o + (bh * S * M + m) * D + d;
+    const int64_t step = static_cast<int64_t>(M) * D;
+#pragma unroll 8
     for (int s = 0; s < S; ++s) {
-      const float w = (mx == -INFINITY) ? 0.f : expf(l[static_cast<int64_t>(s) * M] - mx);
-      acc += w * part_o[((bh * S + s) * M + m) * D + d];
+      const float w = s < CACHED ? w_sh[s]
+                                 : ((mx == -INFINITY) ? 0.f : expf(l[static_cast<int64_t>(s) * M] - mx));
+      acc += w * po[s * step];
     }
     const float out = denom > 0.f ? acc / denom : 0.f;
     uint16_t* dst = static_cast<uint16_t*>(o) + b * o_sb + h * o_sh + m * o_sm + d;
@@ -201,7 +236,7 @@ __global__ void splitkv_combine_kernel(const float* __restrict__ part_o, const f
       *dst = *reinterpret_cast<uint16_t*>(&v);
     }
   }
-  if (threadIdx.x == 0) lse[row] = denom > 0.f ? mx + logf(denom) : -INFINITY;
+  if (tid == 0) lse[row] = denom > 0.f ? mx + logf(denom) : -INFINITY;
 }
 
 static int launch_splitkv_combine(const b200attn_splitkv_params* p, bool bf16, unsigned rows,
