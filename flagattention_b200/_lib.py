@@ -99,7 +99,6 @@ class SelftestParams(Structure):
         ("a_chunk_steps", c_int32), ("b_chunk_steps", c_int32),
         ("a_chunk_bytes", c_int32), ("b_chunk_bytes", c_int32),
         ("status", c_void_p),
-        ("repeat", c_int32), ("cycles", c_void_p),
     ]
 
 
@@ -127,6 +126,7 @@ SYMBOLS = {
     "b200attn_abi_version": (c_int32, []),
     "b200attn_last_error": (c_char_p, []),
     "b200attn_umma_selftest": (c_int32, [POINTER(SelftestParams), c_void_p]),
+    "b200attn_wait_timeout_selftest": (c_int32, [c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "b200attn_work_order_selftest": (c_int32, [c_int32, c_int32, c_int32]),
 }
 

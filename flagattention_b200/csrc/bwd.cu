@@ -8,17 +8,6 @@ namespace b200attn {
 
 static int pad128(int m) { return (m + 127) / 128 * 128; }
 
-#ifdef B200ATTN_TIMING
-static long long* g_trace_dev = nullptr;
-static long long* trace_buffer() {
-  if (g_trace_dev == nullptr) {
-    cudaMalloc(&g_trace_dev, sizeof(long long) * 4 * 8192);
-    cudaMemset(g_trace_dev, 0, sizeof(long long) * 4 * 8192);
-  }
-  return g_trace_dev;
-}
-#endif
-
 static int check_common(const char* who, int B, int Hq, int Hkv, int M, int N, int D, int dtype) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || M <= 0 || N <= 0) {
     set_error("%s: B, Hq, Hkv, M, N must be positive", who);
@@ -129,9 +118,6 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
     a.drop.mask_words = cdiv(p->N, 32);
   }
   a.status = p->status;
-#ifdef B200ATTN_TIMING
-  a.trace = trace_buffer();
-#endif
 
   kv.args = a;
   kv.args.out1 = p->dk.ptr;
@@ -220,9 +206,6 @@ static int run_total(const b200attn_total_params* p, float2* stats, cudaStream_t
   a.qk_scale = p->sm_scale * 1.4426950408889634f;
   a.drop = make_dropout_ctx(0.f, 0, 0);
   a.status = p->status;
-#ifdef B200ATTN_TIMING
-  a.trace = nullptr;
-#endif
   L.args = a;
   L.args.n_zblocks = cdiv(p->N, 128);
   L.args.grid_chunk = grid_chunk(1, 2ll * p->M * D, a.causal != 0);
@@ -396,11 +379,3 @@ extern "C" int b200attn_total_attention_static(const b200attn_total_params* p, v
     default: return run_total<128>(p, stats, stream);
   }
 }
-
-#ifdef B200ATTN_TIMING
-// Developer build only: copies the clock64() stamps of the last backward-family launch.
-extern "C" int b200attn_debug_read_trace(long long* host_buf) {
-  if (b200attn::g_trace_dev == nullptr) return -1;
-  return cudaMemcpy(host_buf, b200attn::g_trace_dev, sizeof(long long) * 4 * 8192, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -3;
-}
-#endif

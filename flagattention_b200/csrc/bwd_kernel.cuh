@@ -46,14 +46,6 @@ namespace b200attn {
 
 enum BwdMode : int { MODE_KV = 0, MODE_Q = 1, MODE_TOTAL = 2 };
 
-#ifdef B200ATTN_TIMING
-// Developer build only: per-phase clock64() stamps of block 0 (softmax warp 0 and the MMA thread).
-#define B200ATTN_STAMP(who, idx) \
-  do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (idx) < 8192 && args.trace) args.trace[(who) * 8192 + (idx)] = clock64(); __syncwarp(); } while (0)
-#else
-#define B200ATTN_STAMP(who, idx) do {} while (0)
-#endif
-
 struct BwdArgs {
   void* out1;  // MODE_KV: dK, MODE_Q: dQ
   void* out2;  // MODE_KV: dV
@@ -69,9 +61,6 @@ struct BwdArgs {
   int32_t* status;
   float* dq_acc;        // FUSED: [B, Hq, M, D] fp32, zero before the launch
   int out_tma;          // the 16-bit results leave through shared memory and TMA stores (tmO1, tmO2)
-#ifdef B200ATTN_TIMING
-  long long* trace;
-#endif
 };
 
 template <int D, int MODE, bool FUSED = false>
@@ -208,17 +197,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
     *abort_flag = 1;
   };
   auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while (true) {
-      if (mbar_try_wait(bar, parity)) return true;
-      if ((++spins & 0xffu) == 0u) {
-        if (*abort_flag) return false;
-        if (args.status != nullptr && *reinterpret_cast<volatile int32_t*>(args.status) != 0) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
-      }
-    }
+    return bounded_wait(bar, parity, abort_flag, args.status, WAIT_LIMIT_NS);
   };
 
   if (warp == 9) {
@@ -349,30 +328,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         const int st = i % STAGES;
         if (i + 1 < T) {
           const int st_next = (i + 1) % STAGES;
-          B200ATTN_STAMP(1, 4 * i + 0);
           const bool w = wait(&b_full[st_next], ((i + 1) / STAGES) & 1);
           if (!__all_sync(0xffffffffu, w)) { fail(ST_WAIT_TMA); ok = false; break; }
           if constexpr (FUSED && DQ_ALIASED) {
             // the T2 columns of the other buffer still hold dQ^T of step i - 1 until it is read back
             if (i >= 1) {
-              B200ATTN_STAMP(3, 2 * i + 0);
               const bool w2 = wait(&dq_drained[dq_slot(i - 1)], dq_phase(i - 1));
-              B200ATTN_STAMP(3, 2 * i + 1);
               if (!__all_sync(0xffffffffu, w2)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
             }
           }
           tc_fence_after();
-          B200ATTN_STAMP(1, 4 * i + 1);
           issue_t(buf ^ 1, st_next);
           tc_commit_w(&t_full[buf ^ 1]);
         }
-        B200ATTN_STAMP(1, 4 * i + 2);
         {
           const bool w = wait(&p_ready[buf], (i >> 1) & 1);
           if (!__all_sync(0xffffffffu, w)) { fail(ST_WAIT_SOFTMAX); ok = false; break; }
         }
         tc_fence_after();
-        B200ATTN_STAMP(1, 4 * i + 3);
         if constexpr (MODE == MODE_KV) {
           if constexpr (FUSED) {
             if constexpr (!DQ_ALIASED) {
@@ -407,12 +380,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         const int buf = i & 1;
         const int hh = i / steps_per_head;
         const int col = col_lo + (i - hh * steps_per_head) * STEP;
-        if (warp == 10) B200ATTN_STAMP(2, 4 * i + 0);
         {
+          // The four warps decide together whether to go on: they meet at named barriers below, so
+          // one of them leaving alone would strand the others there. Each warp's own wait is bounded,
+          // hence all four reach this reduction barrier.
           const bool w = wait(&dq_ready[dq_slot(i)], dq_phase(i));
-          if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); break; }
+          uint32_t all_ok;
+          asm volatile(
+              "{\n\t"
+              ".reg .pred p, q;\n\t"
+              "setp.ne.b32 p, %1, 0;\n\t"
+              "bar.red.and.pred q, 2, 128, p;\n\t"
+              "selp.b32 %0, 1, 0, q;\n\t"
+              "}\n"
+              : "=r"(all_ok) : "r"(static_cast<uint32_t>(w)) : "memory");
+          if (!all_ok) { if (!w) fail(ST_WAIT_MMA); break; }
         }
-        if (warp == 10) B200ATTN_STAMP(2, 4 * i + 1);
         tc_fence_after();
         uint32_t v[STEP];
         tmem_ld32(tmem_base + lane_base + dq_col(buf), v);
@@ -420,7 +403,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&dq_drained[dq_slot(i)]);
-        if (warp == 10) B200ATTN_STAMP(2, 4 * i + 2);
         // Out through shared memory, 32 queries at a time: the tile is laid out like the
         // accumulator rows ([query][feature], contiguous in global memory) and one bulk
         // reduction adds it to the fp32 accumulator.
@@ -447,7 +429,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
-        if (warp == 10) B200ATTN_STAMP(2, 4 * i + 3);
       }
       // the staging tile must outlive the reductions that read it
       if (threadIdx.x == 320) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -482,7 +463,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       const int col0 = col_lo + (i - hh * steps_per_head) * STEP + wg * HALF;  // first column of this group
       const int h = h_first + hh;
       const uint32_t t1_addr = tmem_base + lane_base + BUF_BASE + buf * 128;
-      if (warp == 0) B200ATTN_STAMP(0, 4 * i + 0);
       // Dropout decisions for this thread's 32 (row, column) pairs of the step, generated before the
       // T products are awaited so the integer work overlaps the tensor core.
       uint32_t keep_bits = 0xffffffffu;
@@ -521,13 +501,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
       }
       tc_fence_after();
-      if (warp == 0) B200ATTN_STAMP(0, 4 * i + 1);
       uint32_t t1[HALF];
       uint32_t t2[MODE == MODE_TOTAL ? 1 : HALF];
       tmem_ld32(t1_addr + wg * HALF, t1);
       if constexpr (MODE != MODE_TOTAL) tmem_ld32(t1_addr + 64 + wg * HALF, t2);
       tmem_wait_ld();
-      if (warp == 0) B200ATTN_STAMP(0, 4 * i + 2);
 
       // Does this step cross the causal boundary for some row of the block?
       bool diag = false;
@@ -622,7 +600,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       }
       tc_fence_before();
       mbar_arrive(&p_ready[buf]);
-      if (warp == 0) B200ATTN_STAMP(0, 4 * i + 3);
     }
 
     // ------------------------------------------------------------- epilogue

@@ -20,13 +20,12 @@ template <int D, bool BF16, bool DROPOUT, int MODE, bool FUSED = false>
 int launch_bwd_variant(const BwdLaunch& L) {
   auto kernel = bwd_kernel<D, BF16, DROPOUT, MODE, FUSED>;
   constexpr int smem = BwdSmem<D, MODE, FUSED>::TOTAL;
-  static bool attr_done[64] = {};
-  int dev = 0;
-  B200ATTN_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+  static PerDeviceOnce attr_once;  // one per kernel variant
+  const int rc = attr_once.run([&]() -> int {
     B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    if (dev >= 0 && dev < 64) attr_done[dev] = true;
-  }
+    return B200ATTN_OK;
+  });
+  if (rc) return rc;
   kernel<<<L.grid, BwdSmem<D, MODE, FUSED>::THREADS, smem, L.stream>>>(L.tmA1, L.tmA2, L.tmB1, L.tmB2, L.tmO1, L.tmO2, L.args);
   B200ATTN_CUDA_OK(cudaGetLastError());
   return B200ATTN_OK;

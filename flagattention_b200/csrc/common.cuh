@@ -3,12 +3,14 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <mutex>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "../../include/b200attn.h"
+#include "ptx.cuh"
 
 namespace b200attn {
 
@@ -21,6 +23,23 @@ int cuda_fail(cudaError_t e, const char* what);
     cudaError_t _e = (expr);                                    \
     if (_e != cudaSuccess) return ::b200attn::cuda_fail(_e, #expr); \
   } while (0)
+
+// One-time set-up per device (kernel attributes, device properties) that any host thread may
+// trigger: `run(f)` executes `f` once for the current device under std::call_once and hands back its
+// return code to every caller; a failed attempt is remembered and reported again, not retried.
+struct PerDeviceOnce {
+  static constexpr int MAX_DEVICES = 64;
+  std::once_flag flags[MAX_DEVICES];
+  int rc[MAX_DEVICES] = {};
+  template <class F>
+  int run(F&& f) {
+    int dev = 0;
+    B200ATTN_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return f();  // beyond the table: set up on every call
+    std::call_once(flags[dev], [&] { rc[dev] = f(); });
+    return rc[dev];
+  }
+};
 
 // Encodes a 4-D tiled tensor map over a [B, H, rows, D] tensor of 16-bit elements
 // (dims listed innermost first: D, rows, H, B). `box_cols` x `box_rows` is the tile;
@@ -272,6 +291,26 @@ enum : int32_t {
 
 __device__ __forceinline__ void report_status(int32_t* status, int32_t code) {
   if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+// The bounded wait of every kernel role. Returns true once the barrier phase has completed; false
+// when it gives up: after `limit_ns`, or as soon as this CTA (`abort_flag`, in shared memory) or any
+// CTA of any launch sharing the status word has reported a failure. The caller then records its own
+// code (report_status + *abort_flag = 1), leaves its loop and joins the kernel's final barrier, after
+// which TMEM is released.
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                             const int32_t* status, unsigned long long limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0xffu) == 0u) {
+      if (*abort_flag) return false;
+      if (status != nullptr && *reinterpret_cast<const volatile int32_t*>(status) != 0) return false;
+      if (globaltimer_ns() - t0 > limit_ns) return false;
+    }
+  }
 }
 
 }  // namespace b200attn

@@ -1,6 +1,4 @@
 // C entry point of the forward pass: argument validation, TMA descriptors, dispatch on D.
-#include <cstdlib>
-
 #include "decode.cuh"
 #include "fwd_launch.cuh"
 
@@ -42,14 +40,6 @@ static void make_o_tmap(const b200attn_fwd_params* p, FwdLaunch& L) {
 namespace b200attn {
 namespace {
 int cached_sm_count();
-// B200ATTN_FWD_PERSISTENT=0 launches one CTA per work item instead (a measurement aid).
-bool fwd_persistent() {
-  static const bool on = [] {
-    const char* e = std::getenv("B200ATTN_FWD_PERSISTENT");
-    return !(e != nullptr && e[0] == '0');
-  }();
-  return on;
-}
 }  // namespace
 }  // namespace b200attn
 
@@ -151,7 +141,7 @@ extern "C" int b200attn_fwd(const b200attn_fwd_params* p, void* stream) {
   // to even for short masked ones; with a mask over more than 32 K/V tiles the items differ by
   // enough that one CTA per item, placed by the hardware as SMs fall free, measured 3-7 % faster.
   a.n_items = static_cast<int>(static_cast<int64_t>(p->B) * p->Hq * a.n_zblocks);  // range checked above
-  const bool chain = fwd_persistent() && (a.causal == 0 || cdiv(p->N, 128) <= 32);
+  const bool chain = a.causal == 0 || cdiv(p->N, 128) <= 32;
   const int n_ctas = chain ? cached_sm_count() : a.n_items;
   L.grid = dim3(static_cast<unsigned>(a.n_items < n_ctas ? a.n_items : n_ctas));
   L.bf16 = p->dtype == B200ATTN_BF16;
@@ -504,15 +494,19 @@ extern "C" int b200attn_paged_attention(const b200attn_paged_params* p, void* st
 namespace b200attn {
 namespace {
 
+// Multiprocessor count of the current device, looked up once per device.
 int cached_sm_count() {
-  static int counts[64] = {};
+  static PerDeviceOnce once;
+  static int counts[PerDeviceOnce::MAX_DEVICES] = {};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-  if (dev >= 0 && dev < 64 && counts[dev] > 0) return counts[dev];
-  int n = 0;
-  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  if (dev >= 0 && dev < 64) counts[dev] = n;
-  return n;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PerDeviceOnce::MAX_DEVICES) return 148;
+  once.run([&]() -> int {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    counts[dev] = n;   // written inside call_once, read only after it has returned
+    return B200ATTN_OK;
+  });
+  return counts[dev];
 }
 
 }  // namespace

@@ -257,17 +257,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     *abort_flag = 1;
   };
   auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    uint32_t spins = 0;
-    while (true) {
-      if (mbar_try_wait(bar, parity)) return true;
-      if ((++spins & 0xffu) == 0u) {
-        if (*abort_flag) return false;
-        if (args.status != nullptr && *reinterpret_cast<volatile int32_t*>(args.status) != 0) return false;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
-      }
-    }
+    return bounded_wait(bar, parity, abort_flag, args.status, WAIT_LIMIT_NS);
   };
 
   if (warp == 11) {

@@ -18,13 +18,12 @@ int launch_fwd_variant(const FwdLaunch& L) {
   auto kernel = fwd_kernel<D, BF16, DROPOUT>;
   constexpr int smem_max = FwdSmem<D>::TOTAL > FwdSmem<D>::DUAL_TOTAL ? FwdSmem<D>::TOTAL : FwdSmem<D>::DUAL_TOTAL;
   const int smem = L.args.dual_stream ? FwdSmem<D>::DUAL_TOTAL : FwdSmem<D>::TOTAL;
-  static bool attr_done[64] = {};
-  int dev = 0;
-  B200ATTN_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+  static PerDeviceOnce attr_once;  // one per kernel variant
+  const int rc = attr_once.run([&]() -> int {
     B200ATTN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
-    if (dev >= 0 && dev < 64) attr_done[dev] = true;
-  }
+    return B200ATTN_OK;
+  });
+  if (rc) return rc;
   kernel<<<L.grid, 384, smem, L.stream>>>(L.tmQ, L.tmK, L.tmV, L.tmO, L.args);
   B200ATTN_CUDA_OK(cudaGetLastError());
   return B200ATTN_OK;

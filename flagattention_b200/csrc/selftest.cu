@@ -18,8 +18,6 @@ struct SelftestArgs {
   uint64_t a_desc_hi, b_desc_hi;
   int a_step_bytes, b_step_bytes, a_chunk_steps, b_chunk_steps, a_chunk_bytes, b_chunk_bytes;
   int32_t* status;
-  int repeat;            // issue the whole K loop this many times (timing runs)
-  long long* cycles;     // optional: clock64() ticks from first issue to completion
 };
 
 __global__ void __launch_bounds__(128, 1)
@@ -89,8 +87,6 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       failed = 1;
     } else {
       tc_fence_after();
-      const long long t_begin = clock64();
-      for (int rep = 0; rep < args.repeat; ++rep)
       for (int s = 0; s < args.k_steps; ++s) {
         const int a_off = args.a_chunk_steps > 0
                               ? (s / args.a_chunk_steps) * args.a_chunk_bytes +
@@ -105,12 +101,12 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           // A slice goes shared memory -> TMEM with tcgen05.cp, then feeds the MMA from TMEM.
           const uint64_t da = smem_desc(args.a_desc_hi, smem_u32(sA) + a_off);
           asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(tmem_a + s * 8), "l"(da) : "memory");
-          mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, (s > 0 || rep > 0) ? 1u : 0u);
+          mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, s > 0 ? 1u : 0u);
         } else if (args.a_in_tmem) {
-          mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, (s > 0 || rep > 0) ? 1u : 0u);
+          mma_ts(tmem_base, tmem_a + s * 8, db, args.idesc, s > 0 ? 1u : 0u);
         } else {
           const uint64_t da = smem_desc(args.a_desc_hi, smem_u32(sA) + a_off);
-          mma_ss(tmem_base, da, db, args.idesc, (s > 0 || rep > 0) ? 1u : 0u);
+          mma_ss(tmem_base, da, db, args.idesc, s > 0 ? 1u : 0u);
         }
       }
       tc_commit(&bar_mma);
@@ -118,7 +114,6 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         report_status(args.status, ST_WAIT_MMA);
         failed = 1;
       }
-      if (args.cycles != nullptr) *args.cycles = clock64() - t_begin;
     }
   }
   __syncthreads();
@@ -185,16 +180,96 @@ extern "C" int b200attn_umma_selftest(const b200attn_selftest_params* p, void* s
   a.a_chunk_steps = p->a_chunk_steps; a.b_chunk_steps = p->b_chunk_steps;
   a.a_chunk_bytes = p->a_chunk_bytes; a.b_chunk_bytes = p->b_chunk_bytes;
   a.status = p->status;
-  a.repeat = p->repeat > 0 ? p->repeat : 1;
-  a.cycles = p->cycles;
   const int smem_bytes = 65536 + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  rc = attr_once.run([&]() -> int {
     B200ATTN_CUDA_OK(cudaFuncSetAttribute(umma_selftest_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    attr_set = true;
-  }
+    return B200ATTN_OK;
+  });
+  if (rc) return rc;
   umma_selftest_kernel<<<1, 128, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, a);
+  B200ATTN_CUDA_OK(cudaGetLastError());
+  return B200ATTN_OK;
+}
+
+// ------------------------------------------------------------------ the give-up path of the waits
+namespace b200attn {
+
+// Runs the protocol every kernel follows when a wait does not complete, on purpose and harmlessly:
+// the CTA allocates TMEM like the attention kernels, warp 0 waits (bounded_wait, the function those
+// kernels use, with a caller-chosen short limit) on an mbarrier that nothing ever arrives at, records
+// `code` in the status word and raises the CTA's abort flag; the other warps wait on a second barrier
+// with a far longer limit and must be released early by that flag. All warps then meet at the final
+// barrier and TMEM is released. `out[0]` = 1 if warp 0's wait gave up, `out[1]` = number of other
+// warps that were released by the abort flag, `out[2]` = nanoseconds warp 0 waited.
+__global__ void __launch_bounds__(128, 1)
+wait_timeout_selftest_kernel(unsigned long long limit_ns, int32_t code, int32_t* status, long long* out) {
+  __shared__ uint64_t never_a, never_b;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag_s;
+  __shared__ int released;
+  volatile int* abort_flag = &abort_flag_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&never_a, 1);
+    mbar_init(&never_b, 1);
+    abort_flag_s = 0;
+    released = 0;
+    fence_barrier_init();
+  }
+  __syncwarp();
+  if (warp == 0) {
+    tmem_alloc(&tmem_slot, 32);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  if (warp == 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    const bool w = bounded_wait(&never_a, 0, abort_flag, nullptr, limit_ns);
+    const unsigned long long waited = globaltimer_ns() - t0;
+    if (!__all_sync(0xffffffffu, w)) {
+      if (lane == 0) {
+        report_status(status, code);
+        *abort_flag = 1;
+        out[0] = 1;
+        out[2] = static_cast<long long>(waited);
+      }
+    }
+  } else {
+    // 100 x the short limit: only the abort flag can end this wait in time
+    const bool w = bounded_wait(&never_b, 0, abort_flag, nullptr, 100ull * limit_ns);
+    if (!__all_sync(0xffffffffu, w) && lane == 0 && *abort_flag) atomicAdd(&released, 1);
+  }
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  if (threadIdx.x == 0) out[1] = released;
+  if (warp == 0) tmem_dealloc(tmem_base, 32);
+}
+
+}  // namespace b200attn
+
+extern "C" int b200attn_wait_timeout_selftest(int32_t limit_us, int32_t code, int32_t* status, long long* out,
+                                              void* stream) {
+  using namespace b200attn;
+  if (status == nullptr || out == nullptr) {
+    set_error("wait_timeout_selftest: null argument");
+    return B200ATTN_EINVAL;
+  }
+  if (limit_us < 1 || limit_us > 1000) {
+    set_error("wait_timeout_selftest: limit must be 1..1000 microseconds (got %d)", limit_us);
+    return B200ATTN_EINVAL;
+  }
+  if (code < 1 || code > 4) {
+    set_error("wait_timeout_selftest: code must be one of the kernels' status codes 1..4");
+    return B200ATTN_EINVAL;
+  }
+  wait_timeout_selftest_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<unsigned long long>(limit_us) * 1000ull, code, status, out);
   B200ATTN_CUDA_OK(cudaGetLastError());
   return B200ATTN_OK;
 }

@@ -13,35 +13,40 @@ import os
 import torch
 
 from . import _lib
+from . import status as _status
 from .rng_state import as_u64, reserve_philox_stream
 from .split_kv import choose_num_splits
+from .status import check_device_status
 
-__all__ = ["flash_attention", "FlashAttentionFunction", "check_device_status"]
+__all__ = ["flash_attention", "FlashAttentionFunction", "check_device_status", "get_fwd_config",
+           "get_bwd_config"]
 
 _SUPPORTED_HEAD_DIMS = (16, 32, 64, 128)
 # Largest dropout keep-decision cache (bytes, one bit per attention score) handed from forward to backward.
 _KEEP_MASK_LIMIT = 1 << 30
-_status_words: dict[int, torch.Tensor] = {}
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    word = _status_words.get(idx)
-    if word is None:
-        word = torch.zeros(1, dtype=torch.int32, device=device)
-        _status_words[idx] = word
-    return word
+    """The device's status word, after a non-blocking look at what earlier launches reported
+    (``status.poll``): a kernel that gave up on a bounded wait makes one of the next calls raise."""
+    return _status.poll(device)
 
 
-def check_device_status(device=None) -> None:
-    """Synchronises and raises if any kernel launched so far on ``device`` gave up on a bounded
-    device-side wait (the kernels never spin forever; they record a code and exit instead)."""
-    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    word = _status_word(device)
-    code = int(word.item())
-    if code != 0:
-        word.zero_()
-        raise RuntimeError(f"b200attn kernel reported device-side wait timeout (code {code})")
+def get_fwd_config(B, H, M, N, D, causal):
+    """Counterpart of the reference's tile-configuration hook (``flash.py:311-342``): returns
+    ``(BLOCK_M, BLOCK_N, num_stages, num_warps)`` of the forward kernel that would run. The reference
+    documents its hook as replaceable at run time (``examples/use_cutom_config_func.py:18-23`` assigns
+    ``flag_attn.flash.get_fwd_config``). Here tile shapes are template parameters of the CUDA kernels,
+    so the function reports them and assigning another one is accepted and has no effect."""
+    stages = 2 if D == 128 else (3 if D == 64 else 4)
+    return (256, 128, stages, 12)   # two 128-row query tiles per CTA, 128-key K/V tiles, 384 threads
+
+
+def get_bwd_config(B, H, M, N, D, causal):
+    """Counterpart of the reference's backward hook (``flash.py:514-539``); see ``get_fwd_config``.
+    The backward keeps 128 rows resident per CTA and streams 64 columns per step."""
+    fused = D in (64, 128)
+    return (128, 64, 3 if D == 128 else 4, 14 if fused else 10)
 
 
 def _tma_ready(x: torch.Tensor) -> torch.Tensor:
@@ -57,10 +62,6 @@ def _tma_ready(x: torch.Tensor) -> torch.Tensor:
                 ok = False
                 break
     return x if ok else x.contiguous()
-
-
-def _vec_ready(x: torch.Tensor) -> torch.Tensor:
-    return _tma_ready(x)
 
 
 _SM_COUNT = {}
@@ -89,12 +90,14 @@ def _split_kv_forward(lib, q, k, v, causal, sm_scale, num_sms, stream, status):
     o = torch.empty((B, H, M, D), dtype=q.dtype, device=device)
     rows = B * H * M
     if S > 1:
-        # one fp32 allocation: per-split outputs (16-byte aligned rows) | per-split normalisers |
-        # log-normaliser
-        buf = torch.empty(rows * (S * D + S + 1), dtype=torch.float32, device=device)
+        # one fp32 scratch allocation: per-split outputs (16-byte aligned rows) | per-split
+        # normalisers. The log-normaliser is a tensor of its own: autograd saves it and callers may
+        # keep it, which must not keep the partial outputs alive (the reference frees its partials
+        # right after the combine).
+        buf = torch.empty(rows * (S * D + S), dtype=torch.float32, device=device)
         part_o_ptr = buf.data_ptr()
         part_l_ptr = part_o_ptr + 4 * rows * S * D
-        L = buf[rows * (S * D + S):].view(B, H, M)
+        L = torch.empty((B, H, M), device=device, dtype=torch.float32)
     elif (H // Hk) * M <= 2:
         L = torch.empty((B, H, M), device=device, dtype=torch.float32)
         part_o_ptr = part_l_ptr = L.data_ptr()  # unused by the single-split streaming kernel
@@ -257,7 +260,7 @@ class FlashAttentionFunction(torch.autograd.Function):
         device = q.device
         if do.dtype != q.dtype:
             do = do.to(q.dtype)
-        do = _vec_ready(do)
+        do = _tma_ready(do)
         lib = _lib.load()
         with torch.cuda.device(device):
             stream = _lib.current_stream_ptr(device)

@@ -20,6 +20,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
+from .status import poll as _status_word
 
 
 LAUNCHES = 0  # kernels launched by this module in this process (read by the benchmark)
@@ -67,7 +68,7 @@ def _cuda_partial(q, k, v, causal, sm_scale):
     lse = torch.empty((B, Hq, M), dtype=torch.float32, device=q.device)
     p = _lib.FwdParams(_lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), lse.data_ptr(),
                        B, Hq, Hk, M, N, D, _lib.dtype_code(q.dtype), _lib.F32, int(causal), float(sm_scale),
-                       0.0, 0, 0, None)
+                       0.0, 0, 0, _status_word(q.device).data_ptr())
     _lib.check(lib.b200attn_fwd(p, _lib.current_stream_ptr(q.device)), "b200attn_fwd")
     global LAUNCHES
     LAUNCHES += 1

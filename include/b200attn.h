@@ -265,11 +265,18 @@ typedef struct {
   int32_t a_chunk_steps, b_chunk_steps; /* K steps per TMA chunk (0 = all in one) */
   int32_t a_chunk_bytes, b_chunk_bytes; /* byte jump between chunks                */
   int32_t* status;
-  int32_t repeat;      /* issue the K loop this many times, accumulating (0 = once)        */
-  long long* cycles;   /* optional device int64: SM clock ticks from first issue to done   */
 } b200attn_selftest_params;
 
 int b200attn_umma_selftest(const b200attn_selftest_params* p, void* stream);
+
+/* Exercises, harmlessly, what every kernel does when one of its bounded device-side waits runs out:
+ * one small CTA waits at most `limit_us` (1..1000) microseconds on a barrier that nothing arrives at,
+ * records `code` (1..4, the kernels' status codes) in `*status`, releases its other warps through the
+ * abort flag, frees its TMEM and returns; the context stays usable. `out` (3 device int64): [0] = 1 if
+ * the wait gave up, [1] = warps released by the abort flag (3 expected), [2] = nanoseconds waited.
+ * No counterpart in the reference. */
+int b200attn_wait_timeout_selftest(int32_t limit_us, int32_t code, int32_t* status, long long* out,
+                                   void* stream);
 
 /* Host-only check (no GPU needed) of the prepared divisions with which the kernels turn a work-item
  * number into (batch, head) pair and row block: `pairs` pairs x `n_z` row blocks, visited in chunks

@@ -13,6 +13,12 @@ if str(ROOT) not in sys.path:
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
+# The unmodified reference, installed by the recipe in BASELINE.md into the git-ignored baseline/_ref
+# (it is not product source). Only the same-GPU A/B tests import it; absent, they skip with a reason.
+REFERENCE_INSTALL = ROOT / "baseline" / "_ref"
+if (REFERENCE_INSTALL / "flag_attn").is_dir() and str(REFERENCE_INSTALL) not in sys.path:
+    sys.path.append(str(REFERENCE_INSTALL))
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
@@ -27,6 +33,18 @@ def _exact_fp32_matmul():
     torch.backends.cuda.matmul.allow_tf32 = False
     yield
     torch.set_float32_matmul_precision(prev)
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean(request):
+    """After every GPU test: no kernel may have given up on a bounded device-side wait. (The kernels
+    record a code in a per-device status word and leave instead of spinning; nothing else would
+    notice, because the outputs of such a launch are simply incomplete.)"""
+    yield
+    if request.node.get_closest_marker("gpu") is not None and torch.cuda.is_available():
+        from flagattention_b200 import status
+        for idx in status.known_devices():
+            status.check_device_status(torch.device("cuda", idx))
 
 
 def _from_bits(arr: np.ndarray, dtype: str) -> torch.Tensor:

@@ -29,20 +29,30 @@ AUX_SHAPES = [(2, 4, 512, 612, 128), (2, 4, 1024, 1034, 64), (2, 4, 2048, 2048, 
               (1, 2, 8192, 8192, 32)]
 DROPOUT_SHAPES = [s if s[2:4] != (4096, 4001) else (2, 4, 4096, 4000, 128) for s in AUX_SHAPES]
 
-# The reference crosses every shape with causal x dtype x layout x input scale; to keep the suite
-# within minutes each (shape, causal, dtype) gets one layout and one scale, cycling through all.
+# The reference crosses every shape with causal x dtype x layout x input scale
+# (tests/flag_attn/test_flash_attention.py:79-104, :174-204); so does _params. _sampled_params gives
+# each (shape, causal, dtype) one layout and one scale, cycling through all, for the tests that the
+# reference does not have and that repeat a case already covered in full.
 _cycle = itertools.cycle(itertools.product(["BHTD", "BTHD"], [1.0, 2.0, 3.0, 4.0]))
 
 
-def _params(shapes):
+def _id(shape, causal, dtype, layout, scale):
+    return (f"{'x'.join(map(str, shape))}-{'c' if causal else 'n'}-{str(dtype)[6:]}-{layout}-s{scale:g}")
+
+
+def _params(shapes, scales=(1.0, 2.0, 3.0, 4.0)):
+    return [pytest.param(*shape, causal, dtype, layout, scale, id=_id(shape, causal, dtype, layout, scale))
+            for shape in shapes for causal in (True, False) for dtype in (torch.float16, torch.bfloat16)
+            for layout in ("BHTD", "BTHD") for scale in scales]
+
+
+def _sampled_params(shapes):
     out = []
     for shape in shapes:
         for causal in (True, False):
             for dtype in (torch.float16, torch.bfloat16):
                 layout, scale = next(_cycle)
-                out.append(pytest.param(*shape, causal, dtype, layout, scale,
-                                        id=f"{'x'.join(map(str, shape))}-{'c' if causal else 'n'}-"
-                                           f"{str(dtype)[6:]}-{layout}-s{scale:g}"))
+                out.append(pytest.param(*shape, causal, dtype, layout, scale, id=_id(shape, causal, dtype, layout, scale)))
     return out
 
 
@@ -64,11 +74,10 @@ SPLIT_SHAPES[7] = (1, 2, 2, 4, 8202, 16)
 SPLIT_SHAPES[16] = (1, 2, 1, 4, 8202, 16)
 
 
-@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,scale",
-                         [p for p in _params(SPLIT_SHAPES)])
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,scale", _params(SPLIT_SHAPES, scales=(10.0,)))
 def test_attention_splitkv(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
     # Decode-like shapes take the split-KV branch (tests/flag_attn/test_flash_attention.py:127-172).
-    q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, dtype, layout, 10.0, seed=10086)
+    q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, dtype, layout, scale, seed=10086)
     o_ref = attention_forward(q, k, v, causal, upcast=True)
     o_low = attention_forward(q, k, v, causal, upcast=False)
     o = flash_attention(q, k, v, causal)
@@ -120,7 +129,7 @@ def test_attention_bwd(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
 
 
 @pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,dtype,layout,scale",
-                         [p for p in _params([s for s in BWD_SHAPES if s[5] in (64, 128)])])
+                         _sampled_params([s for s in BWD_SHAPES if s[5] in (64, 128)]))
 def test_attention_bwd_deterministic_mode(B, Hq, Hk, M, N, D, causal, dtype, layout, scale):
     """Under torch.use_deterministic_algorithms(True) head dimensions 128 and 64 use the two separate
     backward kernels instead of the fused pass with global reductions: same parity rule, and two runs
@@ -148,8 +157,8 @@ def test_attention_bwd_deterministic_mode(B, Hq, Hk, M, N, D, causal, dtype, lay
 
 @pytest.mark.parametrize("B,H,M,N,D,dtype,layout,scale", [
     pytest.param(*s, dt, lay, sc, id=f"{'x'.join(map(str, s))}-{str(dt)[6:]}-{lay}-s{sc:g}")
-    for s, (dt, lay, sc) in zip(AUX_SHAPES * 2, itertools.cycle(itertools.product(
-        [torch.float16, torch.bfloat16], ["BHTD", "BTHD"], [1.0, 2.0, 3.0, 4.0])))])
+    for s in AUX_SHAPES for dt in (torch.float16, torch.bfloat16) for lay in ("BHTD", "BTHD")
+    for sc in (1.0, 2.0, 3.0, 4.0)])
 def test_attention_with_aux_outs(B, H, M, N, D, dtype, layout, scale):
     q, k, v, _ = make_qkv(B, H, H, M, N, D, dtype, layout, scale, seed=10086)
     o_ref, l_ref, t_ref = attention_forward(q, k, v, False, upcast=True, return_log_normalizer=True,
@@ -168,15 +177,12 @@ def test_attention_with_aux_outs(B, H, M, N, D, dtype, layout, scale):
 
 
 def _dropout_params():
-    out = []
-    cyc = itertools.cycle(itertools.product([0.5, 0.8], [True, False], [torch.float16, torch.bfloat16],
-                                            ["BHTD", "BTHD"], [1.0, 2.0]))
-    for shape in DROPOUT_SHAPES * 4:
-        p, causal, dtype, layout, scale = next(cyc)
-        out.append(pytest.param(*shape, p, causal, dtype, layout, scale,
-                                id=f"{'x'.join(map(str, shape))}-p{p}-{'c' if causal else 'n'}-"
-                                   f"{str(dtype)[6:]}-{layout}-s{scale:g}"))
-    return out
+    # the reference's cross product (tests/flag_attn/test_flash_attention.py:298-316, :340-358)
+    return [pytest.param(*shape, p, causal, dtype, layout, scale,
+                         id=f"{'x'.join(map(str, shape))}-p{p}-{'c' if causal else 'n'}-"
+                            f"{str(dtype)[6:]}-{layout}-s{scale:g}")
+            for shape in DROPOUT_SHAPES for p in (0.5, 0.8) for causal in (True, False)
+            for dtype in (torch.float16, torch.bfloat16) for layout in ("BHTD", "BTHD") for scale in (1.0, 2.0)]
 
 
 @pytest.mark.parametrize("B,H,M,N,D,p,causal,dtype,layout,scale", _dropout_params())

@@ -32,19 +32,21 @@ def test_c2_gqa_prefill_train_step():
     o, lse, _, _, _ = flash_attention(q, k, v, causal=True, return_log_normalizer=True)
     dq, dk, dv = torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
     check_device_status()
-    # (a) oracle on batch 1, KV group 3 (query heads 12..15): an independent unit of the problem
-    b, g = 1, 3
-    qs, ks, vs, dos = q[b:b + 1, 4 * g:4 * g + 4].detach(), k[b:b + 1, g:g + 1].detach(), v[b:b + 1, g:g + 1].detach(), do[b:b + 1, 4 * g:4 * g + 4]
-    o_ref, l_ref, _ = attention_forward(qs, ks, vs, True, upcast=True, return_log_normalizer=True)
-    o_low = attention_forward(qs, ks, vs, True, upcast=False)
-    assert_2x_rule("o", o[b:b + 1, 4 * g:4 * g + 4], o_low, o_ref)
-    assert max_abs_diff(lse[b:b + 1, 4 * g:4 * g + 4], l_ref) <= 1e-4
-    rdq, rdk, rdv = attention_backward(qs, ks, vs, dos, True)
-    qa, ka, va = (t.clone().requires_grad_(True) for t in (qs, ks, vs))
-    g_low = torch.autograd.grad(attention_forward(qa, ka, va, True, upcast=False), (qa, ka, va), dos)
-    assert_2x_rule("dq", dq[b:b + 1, 4 * g:4 * g + 4], g_low[0], rdq)
-    assert_2x_rule("dk", dk[b:b + 1, g:g + 1], g_low[1], rdk)
-    assert_2x_rule("dv", dv[b:b + 1, g:g + 1], g_low[2], rdv)
+    # (a) oracle on three (batch, KV group) units (query heads 4g..4g+3), each an independent unit of the problem
+    for b, g in ((1, 3), (0, 0), (3, 7)):
+        hs = slice(4 * g, 4 * g + 4)
+        qs, ks, vs, dos = q[b:b + 1, hs].detach(), k[b:b + 1, g:g + 1].detach(), v[b:b + 1, g:g + 1].detach(), do[b:b + 1, hs]
+        o_ref, l_ref, _ = attention_forward(qs, ks, vs, True, upcast=True, return_log_normalizer=True)
+        o_low = attention_forward(qs, ks, vs, True, upcast=False)
+        assert_2x_rule("o", o[b:b + 1, hs], o_low, o_ref)
+        assert max_abs_diff(lse[b:b + 1, hs], l_ref) <= 1e-4
+        rdq, rdk, rdv = attention_backward(qs, ks, vs, dos, True)
+        qa, ka, va = (t.clone().requires_grad_(True) for t in (qs, ks, vs))
+        g_low = torch.autograd.grad(attention_forward(qa, ka, va, True, upcast=False), (qa, ka, va), dos)
+        assert_2x_rule("dq", dq[b:b + 1, hs], g_low[0], rdq)
+        assert_2x_rule("dk", dk[b:b + 1, g:g + 1], g_low[1], rdk)
+        assert_2x_rule("dv", dv[b:b + 1, g:g + 1], g_low[2], rdv)
+    b, g = 3, 7
     # (b) sharding by (batch, KV group) reproduces the full run bit for bit
     q2, k2, v2 = (t.detach()[b:b + 1, sl].clone().requires_grad_(True)
                   for t, sl in ((q, slice(4 * g, 4 * g + 4)), (k, slice(g, g + 1)), (v, slice(g, g + 1))))
@@ -165,6 +167,15 @@ def test_c5_long_context_causal_forward():
     o_ref = attention_forward(q[:, h:h + 1, sl], k[:, hk:hk + 1, :m0 + r], v[:, hk:hk + 1, :m0 + r], True, upcast=True)
     o_low = attention_forward(q[:, h:h + 1, sl], k[:, hk:hk + 1, :m0 + r], v[:, hk:hk + 1, :m0 + r], True, upcast=False)
     assert_2x_rule("o middle", o[:, h:h + 1, sl], o_low, o_ref)
+    # one more head of every KV group, each on its own band of 256 rows
+    for hk in range(8):
+        h, m0 = hk * 8 + (3 * hk + 1) % 8, 2048 + 3800 * hk
+        sl = slice(m0, m0 + 256)
+        o_ref, l_ref, _ = attention_forward(q[:, h:h + 1, sl], k[:, hk:hk + 1, :m0 + 256], v[:, hk:hk + 1, :m0 + 256], True,
+                                            upcast=True, return_log_normalizer=True)
+        o_low = attention_forward(q[:, h:h + 1, sl], k[:, hk:hk + 1, :m0 + 256], v[:, hk:hk + 1, :m0 + 256], True, upcast=False)
+        assert_2x_rule(f"o head {h}", o[:, h:h + 1, sl], o_low, o_ref)
+        assert max_abs_diff(lse[:, h:h + 1, sl], l_ref) <= 2e-4
     # V = 1 -> O = 1 everywhere
     o1 = flash_attention(q, k, torch.ones_like(v), causal=True)
     assert max_abs_diff(o1, torch.ones_like(o1)) <= 2 ** -7

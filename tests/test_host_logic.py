@@ -120,3 +120,28 @@ def test_prepared_work_item_decode_matches_plain_division():
                               (4096, 4, 1), (3, 1000, 2), (255, 17, 256), (2048, 16, 4096)]:
         assert lib.b200attn_work_order_selftest(pairs, n_z, chunk) == 0, (pairs, n_z, chunk)
     assert lib.b200attn_work_order_selftest(0, 1, 1) < 0
+
+
+def test_tile_config_hooks_exist_and_may_be_assigned():
+    """The reference documents `flash.get_fwd_config` / `get_bwd_config` as replaceable at run time
+    (`flash.py:309-342`, `:512-539`; `examples/use_cutom_config_func.py:18-23` assigns one). Here they
+    report the compiled tile shapes; assigning a replacement must be accepted (and changes nothing)."""
+    from flagattention_b200 import flash
+    fwd = flash.get_fwd_config(2, 16, 4096, 4096, 128, True)
+    bwd = flash.get_bwd_config(2, 16, 4096, 4096, 128, True)
+    assert len(fwd) == 4 and len(bwd) == 4 and all(isinstance(x, int) for x in fwd + bwd)
+    saved = flash.get_fwd_config, flash.get_bwd_config
+    try:
+        def get_fwd_config(B, H, M, N, D, causal):
+            return (64, 64, 1, 4)
+        flash.get_fwd_config = get_fwd_config          # what the reference's example does
+        flash.get_bwd_config = lambda *a: (64, 64, 1, 4)
+        assert flash.get_fwd_config(2, 16, 4096, 4096, 128, True) == (64, 64, 1, 4)
+    finally:
+        flash.get_fwd_config, flash.get_bwd_config = saved
+
+
+def test_wait_timeout_selftest_validates_its_arguments():
+    lib = _lib.load()
+    assert lib.b200attn_wait_timeout_selftest(100, 1, None, None, None) == -1
+    assert b"null" in lib.b200attn_last_error()

@@ -78,3 +78,49 @@ def test_install_and_uninstall(fake_flag_attn):
     assert fa.paged_attention() == "generic-paged"
     assert fa.flash_attention() == "generic"
     assert fa.flash_attention_split_kv() == "generic-split"
+
+
+def _real_reference_root():
+    """Directory holding the unmodified reference package: $FLAG_ATTN_REF (a checkout's `src`) or the
+    install under baseline/_ref."""
+    import os
+    from conftest import REFERENCE_INSTALL
+    env = os.environ.get("FLAG_ATTN_REF")
+    for cand in ([env] if env else []) + [str(REFERENCE_INSTALL)]:
+        if cand and os.path.isdir(os.path.join(cand, "flag_attn", "runtime", "backend")):
+            return cand
+    return None
+
+
+@pytest.mark.skipif(_real_reference_root() is None,
+                    reason="no reference package: set FLAG_ATTN_REF or install baseline/_ref (BASELINE.md)")
+def test_install_into_the_reference_registry_itself(monkeypatch):
+    """The same round trip through the reference's real facade and registry
+    (`src/flag_attn/__init__.py:123-135`, `runtime/backend/op_registry.py:18-60`). No kernel runs: the
+    registry only resolves callables. The detected vendor of a machine without a GPU is "cpu", so the
+    test pins the vendor name the way `resolve_operator(..., vendor=...)` allows."""
+    root = _real_reference_root()
+    for mod in [m for m in sys.modules if m == "flag_attn" or m.startswith("flag_attn.")]:
+        monkeypatch.delitem(sys.modules, mod)
+    monkeypatch.syspath_prepend(root)
+    monkeypatch.setattr(sys, "dont_write_bytecode", True)
+    fa = importlib.import_module("flag_attn")
+    runtime = importlib.import_module("flag_attn.runtime")
+    import types
+    monkeypatch.setattr(runtime, "device", types.SimpleNamespace(vendor_name="nvidia", name="cuda"))
+    from flagattention_b200 import (flash_attention, flash_attention_split_kv, paged_attention,
+                                    piecewise_attention, plugin)
+    plugin.uninstall()
+    generic = fa.flash_attention
+    assert generic.__module__.startswith("flag_attn")
+    plugin.install()
+    try:
+        assert fa.flash_attention is flash_attention
+        assert fa.flash_attention_split_kv is flash_attention_split_kv
+        assert fa.paged_attention is paged_attention
+        assert fa.piecewise_attention is piecewise_attention
+    finally:
+        plugin.uninstall()
+    assert fa.flash_attention is generic
+    for mod in [m for m in sys.modules if m == "flag_attn" or m.startswith("flag_attn.")]:
+        sys.modules.pop(mod, None)
