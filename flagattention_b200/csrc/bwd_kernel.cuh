@@ -521,6 +521,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
         }
         diag = d_lo_blk < args.d_min || d_hi_blk >= args.d_max;
       }
+      // Keys past the end of the sequence: their K and V rows are zero-filled by TMA, so the recomputed
+      // score is 0 and P = exp(-lse), which is not zero and overflows the 16-bit P (and with it dS, and
+      // through 0 x inf the whole dQ row) when a query's log-normaliser is very negative. Mask them like
+      // hidden entries.
+      if constexpr (MODE == MODE_Q) {
+        diag = diag || col0 + HALF > args.N;
+      } else {
+        diag = diag || r0 + 128 > args.N;
+      }
       const float4* stats4 = reinterpret_cast<const float4*>(sB + st * Sm::STAGE_BYTES + Sm::N_B * Sm::B_TILE_BYTES) +
                              wg * (HALF / 2);
 #pragma unroll
@@ -543,12 +552,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           bool vis_a, vis_b;
           if constexpr (MODE == MODE_Q) {
             const int d = row + P_SEQ - (col0 + c);
-            vis_a = d >= args.d_min && d < args.d_max;
-            vis_b = d - 1 >= args.d_min && d - 1 < args.d_max;
+            vis_a = d >= args.d_min && d < args.d_max && col0 + c < args.N;
+            vis_b = d - 1 >= args.d_min && d - 1 < args.d_max && col0 + c + 1 < args.N;
           } else {
             const int d = col0 + c + P_SEQ - row;
-            vis_a = d >= args.d_min && d < args.d_max;
-            vis_b = d + 1 >= args.d_min && d + 1 < args.d_max;
+            vis_a = d >= args.d_min && d < args.d_max && row < args.N;
+            vis_b = d + 1 >= args.d_min && d + 1 < args.d_max && row < args.N;
           }
           p_a = vis_a ? p_a : 0.f;
           p_b = vis_b ? p_b : 0.f;

@@ -97,7 +97,7 @@ struct FwdSmem {
   static constexpr int BAR_OFFSET = Q_BYTES + 2 * KV_BYTES + O_STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;  // barriers + alignment slack
   // Dual-stream mode: one Q tile, as deep a ring as fits (at most 8 stages: the barrier block
-  // holds 14 + 4 * stages barriers in 512 bytes).
+  // holds 18 + 4 * stages barriers in 512 bytes).
   static constexpr int MAX_TOTAL = 232448;
   static constexpr int DUAL_STAGES_FIT = (MAX_TOTAL - 1536 - TileCfg<D>::TILE_BYTES) / (2 * TileCfg<D>::TILE_BYTES);
   static constexpr int DUAL_STAGES = DUAL_STAGES_FIT > 8 ? 8 : DUAL_STAGES_FIT;
@@ -118,7 +118,7 @@ static constexpr int BAND_INF = 1 << 30;
 // dimension, the fewer tensor-core cycles stand against the 16-per-clock special-function unit, so
 // the larger the share that pays.
 #ifndef B200ATTN_FWD_POLY_MASK_D128
-#define B200ATTN_FWD_POLY_MASK_D128 0x11u
+#define B200ATTN_FWD_POLY_MASK_D128 0x00u
 #endif
 #ifndef B200ATTN_FWD_POLY_MASK_SMALL_D
 #define B200ATTN_FWD_POLY_MASK_SMALL_D 0x11u
@@ -128,7 +128,15 @@ struct PolyMask {
   static constexpr uint32_t value = D >= 128 ? B200ATTN_FWD_POLY_MASK_D128 : B200ATTN_FWD_POLY_MASK_SMALL_D;
 };
 
-template <int D, bool BF16, bool DROPOUT>
+// SPLIT64 (D = 128, plain mode only: no head packing, no paged cache): the softmax works on 64 keys at a
+// time and each query tile's 128 S columns hold two 64-key score buffers, so Q K^T of sub-step u + 2 is
+// issued right behind P V of sub-step u and is complete long before the softmax group has finished
+// sub-step u + 1: the group never waits for its own tile's tensor-core work (with one 128-column S per
+// tile, as below, softmax -> P V -> next Q K^T -> softmax of one tile are strictly serial and the tensor
+// pipe idles while a tile's softmax runs). P of a sub-step overwrites the first 32 columns of its own
+// buffer. The accumulator is no longer quiescent while a softmax step runs, so the (rare) rescale of
+// O first waits on `pv_done` for the previous sub-step's P V.
+template <int D, bool BF16, bool DROPOUT, bool SPLIT64 = false>
 __global__ void __launch_bounds__(384, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -137,6 +145,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   using Sm = FwdSmem<D>;
   constexpr int STAGES = Sm::STAGES;
   constexpr int BLOCK = Cfg::BLOCK;
+  constexpr int SUB = 64;  // SPLIT64: keys per softmax sub-step
+  static_assert(!SPLIT64 || D == 128, "the 64-key pipeline exists for D = 128");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -145,23 +155,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   // tile (both query tiles hold the same rows), no output staging (its partial outputs are fp32 and
   // stored directly) and spends the space on a deeper ring.
   const bool dual = args.pack_heads > 0 && args.dual_stream != 0;
-  const int stages = dual ? args.ring_stages : STAGES;
+  // SPLIT64: the same ring memory holds twice as many slots of 64 keys each, so that a slot is
+  // reloaded four sub-steps before its next use (with whole 128-key tiles in two slots the loads of
+  // the faster pipeline arrive late).
+  constexpr int SLOT_BYTES = SPLIT64 ? Cfg::TILE_BYTES / 2 : Cfg::TILE_BYTES;
+  constexpr int SLOT_CHUNK_BYTES = SPLIT64 ? Cfg::CHUNK_BYTES / 2 : Cfg::CHUNK_BYTES;  // one [rows x CHUNK] box
+  const int stages = dual ? args.ring_stages : (SPLIT64 ? 2 * STAGES : STAGES);
   uint8_t* sQ = smem;
   uint8_t* sK = smem + (dual ? 1 : 2) * Cfg::TILE_BYTES;
-  uint8_t* sV = sK + stages * Cfg::TILE_BYTES;
-  uint8_t* sO = sV + stages * Cfg::TILE_BYTES;
+  uint8_t* sV = sK + stages * SLOT_BYTES;
+  uint8_t* sO = sV + stages * SLOT_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sO + (dual ? 0 : Sm::O_STAGE_BYTES));
   uint64_t* q_full = bars;                  // [2]
   uint64_t* k_full = bars + 2;              // [stages]
   uint64_t* k_empty = k_full + stages;      // [stages]
   uint64_t* v_full = k_empty + stages;      // [stages]
   uint64_t* v_empty = v_full + stages;      // [stages]
-  uint64_t* s_full = v_empty + stages;      // [2]
-  uint64_t* p_half = s_full + 2;            // [2 tiles][2 halves]
+  uint64_t* s_full = v_empty + stages;      // [2] (SPLIT64: [2 tiles][2 buffers])
+  uint64_t* p_half = s_full + 4;            // [2 tiles][2 halves] (SPLIT64: P of buffer 0 / 1)
   uint64_t* o_full = p_half + 4;            // [2]
   uint64_t* q_empty = o_full + 2;           // [2]
   uint64_t* o_sync = q_empty + 2;           // [2] the four warps of a tile meet here around the output staging
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_sync + 2);
+  uint64_t* pv_done = o_sync + 2;           // [2] SPLIT64: every P V issued so far for the tile has completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -175,6 +191,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     int b, hk, h, m0, split, N_ctx, P_SEQ;
     int j0;          // first K/V tile the CTA streams
     int n_tiles[2];  // number of K/V tiles each query tile visits
+    int n_sub[2];    // SPLIT64: number of 64-key sub-steps each query tile runs
     int n_max;       // number of K/V tiles the CTA streams
   };
   auto get_item = [&](int id) -> Item {
@@ -208,6 +225,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         n_full = t == 0 ? cdiv(hi_p, BLOCK) : 0;
       }
       it.n_tiles[t] = max(0, min(n_full, j_split + args.tiles_per_split) - it.j0);
+      // (a last half tile that no row of the query tile sees is not computed)
+      it.n_sub[t] = mt < args.M ? max(0, cdiv(min(hi, (j_split + args.tiles_per_split) * BLOCK), SUB) - 2 * it.j0) : 0;
+      if constexpr (SPLIT64) it.n_tiles[t] = (it.n_sub[t] + 1) / 2;
     }
     if (dual) {
       const int n = it.n_tiles[0];
@@ -228,12 +248,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     mbar_init(&q_full[1], 1);
     for (int s = 0; s < stages; ++s) {
       mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
+      mbar_init(&k_empty[s], SPLIT64 ? 2 : 1);
       mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
+      mbar_init(&v_empty[s], SPLIT64 ? 2 : 1);
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
+      mbar_init(&s_full[2 + t], 1);
+      mbar_init(&pv_done[t], 1);
       mbar_init(&p_half[2 * t], 128);
       mbar_init(&p_half[2 * t + 1], 128);
       mbar_init(&o_full[t], 1);
@@ -262,7 +284,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   if (warp == 11) {
     reg_dealloc<80>();
-  } else if (warp == 9 || warp == 10) {
+  } else if (warp == 9 || (!SPLIT64 && warp == 10)) {
     // ------------------------------------------------------------ TMA producers
     // Warp 9 loads Q and streams the K and V tiles (one elected lane). With a paged cache a tile is
     // up to 16 small copies per operand and one thread cannot issue them fast enough, so warp 10
@@ -298,7 +320,31 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           }
           if (!alive) break;
         }
-        if (!paged) {
+        if constexpr (SPLIT64) {
+          // Ring position i of an item holds the keys of sub-step i in its K slot and the values of
+          // sub-step i - 2 in its V slot (Q K^T of sub-step u + 2 is issued together with P V of
+          // sub-step u), behind one pair of barriers (k_full / k_empty). The position runs on across items.
+          const int n_sub_max = max(it.n_sub[0], it.n_sub[1]);
+          const int key0 = it.j0 * BLOCK;
+          for (int i = 0; i < n_sub_max + 2 && alive; ++i) {
+            const bool has_k = i < n_sub_max, has_v = i >= 2;
+            if (!has_k && !has_v) continue;
+            if (st == stages) { st = 0; par ^= 1; }
+            if (!wait(&k_empty[st], par)) { fail(ST_WAIT_EMPTY); alive = false; break; }
+            mbar_expect_tx(&k_full[st], (has_k ? SLOT_BYTES : 0) + (has_v ? SLOT_BYTES : 0));
+            if (has_k) {
+              for (int c = 0; c < Cfg::NCHUNK; ++c)
+                tma_load_4d(sK + st * SLOT_BYTES + c * SLOT_CHUNK_BYTES, &tmK, &k_full[st],
+                            c * Cfg::CHUNK, key0 + i * SUB, it.hk, it.b);
+            }
+            if (has_v) {
+              for (int c = 0; c < Cfg::NCHUNK; ++c)
+                tma_load_4d(sV + st * SLOT_BYTES + c * SLOT_CHUNK_BYTES, &tmV, &k_full[st],
+                            c * Cfg::CHUNK, key0 + (i - 2) * SUB, it.hk, it.b);
+            }
+            ++st;
+          }
+        } else if (!paged) {
           // Dense K/V: one tile = 128 consecutive keys = one box per 64-column chunk.
           for (int j = 0; j < it.n_max; ++j, ++st) {
             if (st == stages) { st = 0; par ^= 1; }
@@ -342,8 +388,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
     }
     __syncwarp();
-  } else if (warp == 8) {
+  } else if (warp == 8 || (SPLIT64 && warp == 10)) {
     // ------------------------------------------------------------- MMA issuer
+    // (SPLIT64: one issuing warp per query tile, warp 8 for tile 0 and warp 10 for tile 1)
     // The whole warp runs this loop with warp-uniform values; one elected lane issues each
     // tcgen05 instruction (see mma_ss_w).
     reg_dealloc<80>();
@@ -362,6 +409,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const uint32_t off = ((s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES +
                               (s % Cfg::STEPS_PER_CHUNK) * 32) >> 4;
         mma_ss_w(tmem_base + t * BLOCK, dq + off, dk + off, IDESC_QK, s > 0 ? 1u : 0u);
+      }
+    };
+    // SPLIT64: S buffer h of tile t (64 fp32 columns) = Q_t x (keys 64 h .. 64 h + 63 of the K tile)^T
+    // SPLIT64: S buffer h of tile t (64 fp32 columns) = Q_t x (the 64 keys in K slot `st`)^T
+    auto issue_qk64 = [&](int t, int st, int h) {
+      constexpr uint32_t IDESC_QK64 = make_idesc(BF16, 128, SUB, false, false);
+      const uint64_t dq = smem_desc(Cfg::KMAJOR_DESC, q_addr + t * Cfg::TILE_BYTES);
+      const uint64_t dk = smem_desc(Cfg::KMAJOR_DESC, k_addr + st * SLOT_BYTES);
+#pragma unroll
+      for (int s = 0; s < D / 16; ++s) {
+        const uint32_t off_q = ((s / Cfg::STEPS_PER_CHUNK) * Cfg::CHUNK_BYTES + (s % Cfg::STEPS_PER_CHUNK) * 32) >> 4;
+        const uint32_t off_k = ((s / Cfg::STEPS_PER_CHUNK) * SLOT_CHUNK_BYTES + (s % Cfg::STEPS_PER_CHUNK) * 32) >> 4;
+        mma_ss_w(tmem_base + t * BLOCK + h * SUB, dq + off_q, dk + off_k, IDESC_QK64, s > 0 ? 1u : 0u);
+      }
+    };
+    // SPLIT64: O_t (+)= P (the first 32 columns of buffer h) x the 64 keys in V slot `st`
+    auto issue_pv64 = [&](int t, int st, bool acc, int h) {
+      constexpr uint64_t V_DESC = make_smem_desc_hi(SLOT_CHUNK_BYTES, 8 * Cfg::ROW_BYTES, Cfg::UMMA_SWZ);
+      const uint64_t dv = smem_desc(V_DESC, v_addr + st * SLOT_BYTES);
+#pragma unroll
+      for (int s = 0; s < SUB / 16; ++s) {
+        mma_ts_w(tmem_base + 2 * BLOCK + t * D, tmem_base + t * BLOCK + h * SUB + s * 8,
+                 dv + ((s * 16 * Cfg::ROW_BYTES) >> 4), IDESC_PV, (acc || s > 0) ? 1u : 0u);
       }
     };
     auto issue_pv = [&](int t, int st, bool acc, int half) {
@@ -401,12 +471,69 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     int st = 0;
     uint32_t ph = 0;
     uint32_t q_ph[2] = {0, 0}, p_ph[2] = {0, 0};
+    uint32_t p_ph_b[2] = {0, 0};       // SPLIT64: phases of the second score buffer's P barriers (p_ph: the first)
+    int ks = 0;                        // SPLIT64: ring position of the next sub-step
+    uint32_t kph = 0;
     for (int k = 0;; ++k) {
       const int id = item_of_round(k);
       if (id >= args.n_items || (k > 0 && *abort_flag)) break;
       const Item it = get_item(id);
       if (it.n_max == 0) continue;
       const int n_max = it.n_max;
+      if constexpr (SPLIT64) {
+        // Sub-step u of a query tile works on keys [64 u, 64 u + 64) of the item's key range, score
+        // buffer u & 1; K slot ks holds the keys of sub-step u + 2 while V slot vs holds those of
+        // sub-step u. Issue order per sub-step and query tile: P V (u), then Q K^T (u + 2) into the
+        // buffer that P V just freed.
+        const int n_sub_max = max(it.n_sub[0], it.n_sub[1]);
+        const int t = warp == 8 ? 0 : 1;   // this warp's query tile
+        const int n_mine = it.n_sub[t];
+        bool ok = true;
+        // Ring positions 0 and 1 hold only keys: the first two Q K^T.
+#pragma unroll
+        for (int u0 = 0; u0 < 2; ++u0) {
+          if (!ok || u0 >= n_sub_max) break;
+          // (every position is awaited before it is released, with or without work on it: a warp whose
+          // tile has nothing to do must not run ahead of the other by a whole pass over the ring)
+          if (!wait_all(&k_full[ks], kph, ST_WAIT_TMA)) { ok = false; break; }
+          if (u0 < n_mine) {
+            if (u0 == 0) {
+              if (!wait_all(&q_full[t], q_ph[t], ST_WAIT_TMA)) { ok = false; break; }
+              q_ph[t] ^= 1;
+            }
+            tc_fence_after();
+            issue_qk64(t, ks, u0);
+            tc_commit_w(&s_full[2 * t + u0]);
+            if (u0 + 1 == n_mine) tc_commit_w(&q_empty[t]);  // the item's last read of Q_t
+          }
+          tc_commit_w(&k_empty[ks]);
+          if (++ks == stages) { ks = 0; kph ^= 1u; }
+        }
+        // Position of sub-step u: values of sub-step u and keys of sub-step u + 2.
+        for (int u = 0; u < n_sub_max && ok; ++u) {
+          const int h = u & 1;
+          if (!wait_all(&k_full[ks], kph, ST_WAIT_TMA)) { ok = false; break; }
+          if (u < n_mine) {
+            if (!wait_all(&p_half[2 * t + h], h ? p_ph_b[t] : p_ph[t], ST_WAIT_SOFTMAX)) { ok = false; break; }
+            if (h) p_ph_b[t] ^= 1; else p_ph[t] ^= 1;
+            tc_fence_after();
+            issue_pv64(t, ks, u > 0, h);
+            if (u + 2 < n_mine) {
+              issue_qk64(t, ks, h);
+              tc_commit_w(&s_full[2 * t + h]);
+              if (u + 3 == n_mine) tc_commit_w(&q_empty[t]);  // the item's last read of Q_t
+            } else if (u + 2 == n_mine) {
+              tc_commit_w(&pv_done[t]);   // the last sub-step's softmax has no later Q K^T to wait on
+            } else {
+              tc_commit_w(&o_full[t]);
+            }
+          }
+          tc_commit_w(&k_empty[ks]);
+          if (++ks == stages) { ks = 0; kph ^= 1u; }
+        }
+        if (!ok) break;
+        continue;
+      }
       if (dual) {
         // Two independent chains: K/V tile j belongs to query tile j & 1. (One item per CTA in
         // this mode, so the phases below start from zero.)
@@ -506,6 +633,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const float qk_scale = args.qk_scale;
     const bool warp_idle = packed && (warp & 3) * 32 >= args.groups * args.M;
     uint32_t s_par = 0, o_par = 0;  // phases of s_full[t] and o_full[t], running on across work items
+    uint32_t s_par1 = 0;            // SPLIT64: phase of the second score buffer's barrier (s_par: the first)
+    uint32_t pv_idx = 0;            // SPLIT64: items of this tile so far with two or more sub-steps = phase of pv_done
     uint32_t sync_par = 0;          // and of o_sync[t]
     // Meeting point of the tile's four warps (an mbarrier rather than bar.sync so that the wait is
     // bounded like every other wait of the kernel).
@@ -550,6 +679,144 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     float m_run = -INFINITY;
     float l_run = 0.f;
 
+    if constexpr (SPLIT64) {
+    const int n_sub = it.n_sub[t];
+    for (int u = 0; u < n_sub; ++u) {
+      const int bsel = u & 1;                       // score buffer of this sub-step
+      const int n0 = (2 * j0 + u) * SUB;            // its first key
+      uint32_t keep_bits[DROPOUT ? 2 : 1];
+      if constexpr (DROPOUT) {
+        const uint64_t base = ctr_row + static_cast<uint64_t>(n0);
+#pragma unroll
+        for (int w = 0; w < 2; ++w) keep_bits[w] = dropout_keep_word(args.drop, base + 32 * w);
+        if (args.drop.keep_mask != nullptr && m_glob < args.M) {
+          const int w0 = n0 >> 5;
+          uint32_t* mk = args.drop.keep_mask +
+                         ((static_cast<int64_t>(b) * args.Hq + h_row) * args.drop.mask_words + w0) * args.M + m_glob;
+#pragma unroll
+          for (int w = 0; w < 2; ++w)
+            if (w0 + w < args.drop.mask_words) mk[static_cast<int64_t>(w) * args.M] = keep_bits[w];
+        }
+      }
+      {
+        const bool w = wait(&s_full[2 * t + bsel], bsel ? s_par1 : s_par);
+        if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
+        if (bsel) s_par1 ^= 1; else s_par ^= 1;
+      }
+      tc_fence_after();
+      const uint32_t tmem_sb = tmem_s + bsel * SUB;
+      uint32_t s[SUB];
+      tmem_ld32(tmem_sb + 0, s + 0);
+      tmem_ld32(tmem_sb + 32, s + 32);
+      tmem_wait_ld();
+
+      if (n0 + SUB > full_upto || n0 < full_from) {
+        // A band edge crosses these 64 keys: this row sees columns [lo_rel, hi_rel). Chunks of 32
+        // columns that every row of the warp sees in full are left alone.
+        const int hi_rel = lim - n0, lo_rel = lo - n0;
+        const int hi_min = __reduce_min_sync(0xffffffffu, hi_rel);
+        const int lo_max = __reduce_max_sync(0xffffffffu, lo_rel);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          if (32 * c + 32 > hi_min || 32 * c < lo_max) {
+#pragma unroll
+            for (int i = 32 * c; i < 32 * c + 32; ++i)
+              if (i >= hi_rel || i < lo_rel) s[i] = 0xff800000u;  // -inf
+          }
+        }
+      }
+
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < SUB; i += 8) {
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx0) : "f"(__uint_as_float(s[i + 0])), "f"(__uint_as_float(s[i + 1])));
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx1) : "f"(__uint_as_float(s[i + 2])), "f"(__uint_as_float(s[i + 3])));
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx2) : "f"(__uint_as_float(s[i + 4])), "f"(__uint_as_float(s[i + 5])));
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx3) : "f"(__uint_as_float(s[i + 6])), "f"(__uint_as_float(s[i + 7])));
+      }
+      const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+
+      bool want = false;
+      if (m_run == -INFINITY) {
+        m_run = m_new;  // nothing accumulated yet for this row
+      } else if ((m_new - m_run) * qk_scale > RESCALE_THRESHOLD) {
+        want = true;
+      }
+      if (__any_sync(0xffffffffu, want)) {
+        // The P V of the previous sub-step may still be running: wait until every P V issued for this
+        // tile has completed (the next one cannot be issued before this thread has delivered its P).
+        // `want` implies u >= 1, so the awaited product belongs to this item.
+        // The Q K^T of sub-step u + 1 was issued right behind that P V, so its barrier (awaited again,
+        // and only then consumed, at the start of the next sub-step) certifies it; behind the item's
+        // second-to-last P V, where no Q K^T follows, the issuing warp commits pv_done instead.
+        {
+          const bool w = (u + 1 < n_sub) ? wait(&s_full[2 * t + (bsel ^ 1)], bsel ? s_par : s_par1)
+                                         : wait(&pv_done[t], pv_idx & 1u);
+          if (!__all_sync(0xffffffffu, w)) { if (!w) fail(ST_WAIT_MMA); ok = false; break; }
+        }
+        tc_fence_after();
+        const float alpha = want ? fast_exp2((m_run - m_new) * qk_scale) : 1.0f;
+        if (want) m_run = m_new;
+        l_run *= alpha;
+#pragma unroll
+        for (int c = 0; c < D; c += 16) {
+          uint32_t o[16];
+          tmem_ld16(tmem_o + c, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st16(tmem_o + c, o);
+        }
+      }
+
+      const float m_eff = (m_run == -INFINITY) ? 0.f : m_run;
+      const float neg_ms = -m_eff * qk_scale;
+      const uint64_t scale2 = f2_pack(qk_scale, qk_scale), neg_ms2 = f2_pack(neg_ms, neg_ms);
+      uint64_t sum01 = 0ull, sum23 = 0ull;
+#pragma unroll
+      for (int i = 0; i < SUB; i += 4) {
+        float p0, p1, p2, p3;
+        const uint64_t x01 = f2_fma(f2_pack(__uint_as_float(s[i + 0]), __uint_as_float(s[i + 1])), scale2, neg_ms2);
+        const uint64_t x23 = f2_fma(f2_pack(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), scale2, neg_ms2);
+        if ((PolyMask<D>::value >> ((i >> 1) & 7)) & 1u) {
+          exp2_poly_pair(x01, p0, p1);
+        } else {
+          float x0, x1;
+          f2_unpack(x01, x0, x1);
+          p0 = fast_exp2(x0);
+          p1 = fast_exp2(x1);
+        }
+        if ((PolyMask<D>::value >> (((i >> 1) + 1) & 7)) & 1u) {
+          exp2_poly_pair(x23, p2, p3);
+        } else {
+          float x2, x3;
+          f2_unpack(x23, x2, x3);
+          p2 = fast_exp2(x2);
+          p3 = fast_exp2(x3);
+        }
+        sum01 = f2_add(sum01, f2_pack(p0, p1));
+        sum23 = f2_add(sum23, f2_pack(p2, p3));
+        if constexpr (DROPOUT) {
+          const uint32_t kb = keep_bits[i >> 5] >> (i & 31);
+          if (!(kb & 1u)) p0 = 0.f;
+          if (!(kb & 2u)) p1 = 0.f;
+          if (!(kb & 4u)) p2 = 0.f;
+          if (!(kb & 8u)) p3 = 0.f;
+        }
+        s[i / 2 + 0] = pack2<BF16>(p0, p1);
+        s[i / 2 + 1] = pack2<BF16>(p2, p3);
+      }
+      tmem_st32(tmem_sb, s);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_half[2 * t + bsel]);
+      float sum0, sum1, sum2, sum3;
+      f2_unpack(sum01, sum0, sum1);
+      f2_unpack(sum23, sum2, sum3);
+      l_run += (sum0 + sum1) + (sum2 + sum3);
+    }
+    if (n_sub >= 2) ++pv_idx;
+    } else {
     for (int j = 0; j < nt; ++j) {
       // Dropout decisions of this row for the tile's 128 keys, generated before S is awaited so the
       // integer work overlaps the tensor core instead of extending the softmax phase.
@@ -692,6 +959,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       f2_unpack(sum23, sum2, sum3);
       l_run += (sum0 + sum1) + (sum2 + sum3);
     }
+    }  // !SPLIT64
 
     // ------------------------------------------------------------- epilogue
     if (ok && nt > 0) {

@@ -10,12 +10,13 @@ struct FwdLaunch {
   FwdArgs args;
   dim3 grid;
   bool bf16, dropout;
+  bool split64 = false;  // D = 128, plain mode: the 64-key softmax pipeline (fwd_kernel's SPLIT64)
   cudaStream_t stream;
 };
 
-template <int D, bool BF16, bool DROPOUT>
+template <int D, bool BF16, bool DROPOUT, bool SPLIT64 = false>
 int launch_fwd_variant(const FwdLaunch& L) {
-  auto kernel = fwd_kernel<D, BF16, DROPOUT>;
+  auto kernel = fwd_kernel<D, BF16, DROPOUT, SPLIT64>;
   constexpr int smem_max = FwdSmem<D>::TOTAL > FwdSmem<D>::DUAL_TOTAL ? FwdSmem<D>::TOTAL : FwdSmem<D>::DUAL_TOTAL;
   const int smem = L.args.dual_stream ? FwdSmem<D>::DUAL_TOTAL : FwdSmem<D>::TOTAL;
   static PerDeviceOnce attr_once;  // one per kernel variant
@@ -31,6 +32,12 @@ int launch_fwd_variant(const FwdLaunch& L) {
 
 template <int D>
 int launch_fwd_d(const FwdLaunch& L) {
+  if constexpr (D == 128) {
+    if (L.split64) {
+      if (L.bf16) return L.dropout ? launch_fwd_variant<D, true, true, true>(L) : launch_fwd_variant<D, true, false, true>(L);
+      return L.dropout ? launch_fwd_variant<D, false, true, true>(L) : launch_fwd_variant<D, false, false, true>(L);
+    }
+  }
   if (L.bf16) {
     return L.dropout ? launch_fwd_variant<D, true, true>(L) : launch_fwd_variant<D, true, false>(L);
   }

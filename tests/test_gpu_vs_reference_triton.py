@@ -110,6 +110,21 @@ def test_all_outputs_within_twice_the_triton_error(B, Hq, Hk, M, N, D, causal, d
         _check(name, a, b_, c)
 
 
+def test_ten_key_case_where_the_in_tree_rule_is_decided_by_one_rounding():
+    """B2 Hq4 Hk2 M=10006 N=10 D128 bf16, causal, [B,T,H,D] layout, inputs of seed 10086: the one input
+    of the reference's test grid on which `err <= 2 x err(native-dtype PyTorch)` does not hold for dQ --
+    for the reference's Triton kernel (1.95e-2 against 2 x 7.8e-3) exactly as for this library. Against
+    the Triton kernel's own error, the acceptance rule of this project, it passes."""
+    fa = _reference()
+    q, k, v, do = make_qkv(2, 4, 2, 10006, 10, 128, torch.bfloat16, "BTHD", 1.0, seed=10086, requires_grad=True)
+    ours, theirs = _run_both(fa, q, k, v, do, True, 0.0, False)
+    o_ref = attention_forward(q, k, v, True, upcast=True)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), do)
+    _check("o", ours[0], theirs[0], o_ref)
+    for name, a, b_, c in zip(("dq", "dk", "dv"), ours[5:], theirs[5:], g_ref):
+        _check(name, a, b_, c)
+
+
 # ------------------------------------------------------------------ the five benchmark configurations
 def _oracle_slices(q, k, v, do, causal, p, full_mask, units, bands, want_tot):
     """fp32 oracle on chosen (batch, kv head) units and, within them, query-row bands [r0, r1).
