@@ -452,6 +452,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
     const uint64_t scale2 = f2_pack(qk_scale, qk_scale);
     float tot_sum = 0.f;
     bool ok = true;
+    // The band limits of this thread with "key n < N" folded in, so that masking keys past the end
+    // costs no instruction per score: with keys on the rows a thread past the end sees nothing; with
+    // keys on the columns n < N is the distance bound d = m + P_SEQ - n > m - M.
+    const int my_d_min = MODE == MODE_Q ? max(args.d_min, row - args.M + 1) : args.d_min;
+    const int my_d_max = (MODE != MODE_Q && row >= args.N) ? -BAND_INF - 2 : args.d_max;
 
     // Both groups work on every step: group `wg` owns columns [32*wg, 32*wg + 32) of the step, which
     // halves the latency between the T products and the accumulating products of a step.
@@ -552,12 +557,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           bool vis_a, vis_b;
           if constexpr (MODE == MODE_Q) {
             const int d = row + P_SEQ - (col0 + c);
-            vis_a = d >= args.d_min && d < args.d_max && col0 + c < args.N;
-            vis_b = d - 1 >= args.d_min && d - 1 < args.d_max && col0 + c + 1 < args.N;
+            vis_a = d >= my_d_min && d < my_d_max;
+            vis_b = d - 1 >= my_d_min && d - 1 < my_d_max;
           } else {
             const int d = col0 + c + P_SEQ - row;
-            vis_a = d >= args.d_min && d < args.d_max && row < args.N;
-            vis_b = d + 1 >= args.d_min && d + 1 < args.d_max && row < args.N;
+            vis_a = d >= my_d_min && d < my_d_max;
+            vis_b = d + 1 >= my_d_min && d + 1 < my_d_max;
           }
           p_a = vis_a ? p_a : 0.f;
           p_b = vis_b ? p_b : 0.f;
