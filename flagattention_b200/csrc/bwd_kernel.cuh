@@ -38,6 +38,8 @@
 // queries with (-inf, 0) so that padded and key-less queries contribute exactly zero. The pair
 // layout feeds the packed f32x2 arithmetic of the recompute loop directly.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 #include "fwd_kernel.cuh"
 #include "ptx.cuh"
@@ -537,57 +539,64 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
       }
       const float4* stats4 = reinterpret_cast<const float4*>(sB + st * Sm::STAGE_BYTES + Sm::N_B * Sm::B_TILE_BYTES) +
                              wg * (HALF / 2);
+      // The loop exists twice, with and without the per-score visibility test, chosen once per step:
+      // left as a test of `diag` inside the loop it is compiled into predicated instructions that every
+      // step issues, masked or not (two more operations per pair there cost the whole pass 8 %).
+      auto recompute = [&](auto diag_tag) {
+        constexpr bool DIAG = decltype(diag_tag)::value;
 #pragma unroll
-      for (int c = 0; c < HALF; c += 2) {
-        uint64_t nlse2, ndel2;
-        if constexpr (MODE == MODE_Q) {
-          nlse2 = f2_pack(row_nlse, row_nlse);
-          ndel2 = f2_pack(row_ndelta, row_ndelta);
-        } else {
-          const float4 sv = stats4[c >> 1];
-          nlse2 = f2_pack(sv.x, sv.y);
-          ndel2 = f2_pack(sv.z, sv.w);
-        }
-        // p = exp2(s * qk_scale - lse * log2e) for two columns at once
-        float x_a, x_b;
-        f2_unpack(f2_fma(f2_pack(__uint_as_float(t1[c]), __uint_as_float(t1[c + 1])), scale2, nlse2), x_a, x_b);
-        float p_a = fast_exp2(x_a);
-        float p_b = fast_exp2(x_b);
-        if (diag) {
-          bool vis_a, vis_b;
+        for (int c = 0; c < HALF; c += 2) {
+          uint64_t nlse2, ndel2;
           if constexpr (MODE == MODE_Q) {
-            const int d = row + P_SEQ - (col0 + c);
-            vis_a = d >= my_d_min && d < my_d_max;
-            vis_b = d - 1 >= my_d_min && d - 1 < my_d_max;
+            nlse2 = f2_pack(row_nlse, row_nlse);
+            ndel2 = f2_pack(row_ndelta, row_ndelta);
           } else {
-            const int d = col0 + c + P_SEQ - row;
-            vis_a = d >= my_d_min && d < my_d_max;
-            vis_b = d + 1 >= my_d_min && d + 1 < my_d_max;
+            const float4 sv = stats4[c >> 1];
+            nlse2 = f2_pack(sv.x, sv.y);
+            ndel2 = f2_pack(sv.z, sv.w);
           }
-          p_a = vis_a ? p_a : 0.f;
-          p_b = vis_b ? p_b : 0.f;
-        }
-        if constexpr (MODE == MODE_TOTAL) {
-          tot_sum += p_a + p_b;
-        } else {
-          float dp_a = __uint_as_float(t2[c]);
-          float dp_b = __uint_as_float(t2[c + 1]);
-          float pd_a = p_a, pd_b = p_b;
-          if constexpr (DROPOUT) {
-            const bool keep_a = (keep_bits >> c) & 1u;
-            const bool keep_b = (keep_bits >> (c + 1)) & 1u;
-            pd_a = keep_a ? p_a : 0.f;
-            pd_b = keep_b ? p_b : 0.f;
-            dp_a = keep_a ? dp_a * args.drop.inv_keep : 0.f;
-            dp_b = keep_b ? dp_b * args.drop.inv_keep : 0.f;
+          // p = exp2(s * qk_scale - lse * log2e) for two columns at once
+          float x_a, x_b;
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(t1[c]), __uint_as_float(t1[c + 1])), scale2, nlse2), x_a, x_b);
+          float p_a = fast_exp2(x_a);
+          float p_b = fast_exp2(x_b);
+          if constexpr (DIAG) {
+            bool vis_a, vis_b;
+            if constexpr (MODE == MODE_Q) {
+              const int d = row + P_SEQ - (col0 + c);
+              vis_a = d >= my_d_min && d < my_d_max;
+              vis_b = d - 1 >= my_d_min && d - 1 < my_d_max;
+            } else {
+              const int d = col0 + c + P_SEQ - row;
+              vis_a = d >= my_d_min && d < my_d_max;
+              vis_b = d + 1 >= my_d_min && d + 1 < my_d_max;
+            }
+            p_a = vis_a ? p_a : 0.f;
+            p_b = vis_b ? p_b : 0.f;
           }
-          // dS = P * (dP - delta)
-          float ds_a, ds_b;
-          f2_unpack(f2_mul(f2_pack(p_a, p_b), f2_add(f2_pack(dp_a, dp_b), ndel2)), ds_a, ds_b);
-          t1[c >> 1] = pack2<BF16>(pd_a, pd_b);
-          t2[c >> 1] = pack2<BF16>(ds_a, ds_b);
+          if constexpr (MODE == MODE_TOTAL) {
+            tot_sum += p_a + p_b;
+          } else {
+            float dp_a = __uint_as_float(t2[c]);
+            float dp_b = __uint_as_float(t2[c + 1]);
+            float pd_a = p_a, pd_b = p_b;
+            if constexpr (DROPOUT) {
+              const bool keep_a = (keep_bits >> c) & 1u;
+              const bool keep_b = (keep_bits >> (c + 1)) & 1u;
+              pd_a = keep_a ? p_a : 0.f;
+              pd_b = keep_b ? p_b : 0.f;
+              dp_a = keep_a ? dp_a * args.drop.inv_keep : 0.f;
+              dp_b = keep_b ? dp_b * args.drop.inv_keep : 0.f;
+            }
+            // dS = P * (dP - delta)
+            float ds_a, ds_b;
+            f2_unpack(f2_mul(f2_pack(p_a, p_b), f2_add(f2_pack(dp_a, dp_b), ndel2)), ds_a, ds_b);
+            t1[c >> 1] = pack2<BF16>(pd_a, pd_b);
+            t2[c >> 1] = pack2<BF16>(ds_a, ds_b);
+          }
         }
-      }
+      };
+      if (diag) recompute(std::true_type{}); else recompute(std::false_type{});
       if constexpr (MODE != MODE_TOTAL) {
         // Outputs go over this group's own (already loaded) T1 columns only, so the two groups
         // never touch each other's unread inputs.
