@@ -486,6 +486,34 @@ def c5_sharded_legs(rank, world, device, dist, steps=5):
     return heads, ring_rec
 
 
+def bind_to_gpu_numa_node(local_rank: int):
+    """Best effort: restrict this process to the CPUs that sysfs lists as local to its GPU before any pinned
+    buffer is allocated, so that the host side of the H2D/D2H copies lives on the GPU's own NUMA node (with
+    every rank's buffers on one node the copies of an 8-GPU run share that node's memory bandwidth).
+    Returns a short description for the record, or the reason nothing was changed."""
+    try:
+        prop = torch.cuda.get_device_properties(local_rank)
+        addr = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+        text = Path(f"/sys/bus/pci/devices/{addr}/local_cpulist").read_text().strip()
+        cpus = set()
+        for part in text.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                cpus.update(range(int(a), int(b) + 1))
+            elif part:
+                cpus.add(int(part))
+        allowed = os.sched_getaffinity(0)
+        local = cpus & allowed
+        if not local:
+            return f"unchanged: none of the GPU-local CPUs ({text}) is in this process's affinity mask"
+        if local != allowed:
+            os.sched_setaffinity(0, local)
+        node = Path(f"/sys/bus/pci/devices/{addr}/numa_node").read_text().strip()
+        return f"GPU {addr} numa node {node}: {len(local)} of {len(allowed)} allowed CPUs"
+    except Exception as exc:  # noqa: BLE001
+        return f"unchanged: {exc!r}"[:160]
+
+
 # ------------------------------------------------------------------ main
 def main():
     ap = argparse.ArgumentParser()
@@ -636,9 +664,12 @@ def main():
         if dist is not None:
             dist.destroy_process_group()
         return
+    full_affinity = os.sched_getaffinity(0)
+    numa_note = bind_to_gpu_numa_node(local_rank)
     host_in = [t.cpu().pin_memory() for t in (q, k, v, do)]
     outs = step()
-    host_out = [torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory() for t in outs]
+    host_out = [torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory().zero_() for t in outs]
+    os.sched_setaffinity(0, full_affinity)   # the pages are placed; the CPU legs below use every core again
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = sum(t.numel() * t.element_size() for t in host_out)
     # Copies and compute are pipelined over three streams with double-buffered device inputs, the
@@ -746,6 +777,7 @@ def main():
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_total / K,
                     "h2d_gbs_per_gpu": h2d_gbs, "d2h_gbs_per_gpu": d2h_gbs,
                     "copy_floor_ms_per_step": max(h2d / h2d_gbs, d2h / d2h_gbs) * 1e-6,
+                    "host_numa_binding": numa_note,
                     "note": "copy rates are of each direction by itself, slowest rank, all ranks copying at "
                             "once; the step cannot be faster than the slower direction"},
             "gpu_launches": kernels_per_step(cfg) * K if ring_step is None else ring_launches,

@@ -64,6 +64,7 @@ class BwdParams(Structure):
         ("status", c_void_p),
         ("band", c_int32), ("dist_min", c_int32), ("dist_max", c_int32),
         ("keep_mask", c_void_p),
+        ("dv_accumulate", c_int32),
     ]
 
 
@@ -155,7 +156,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError here means the .so is stale
         fn.restype = restype
         fn.argtypes = argtypes
-    if lib.b200attn_abi_version() != 2:
+    if lib.b200attn_abi_version() != 3:
         raise RuntimeError("libb200attn.so ABI version mismatch; rebuild the library")
     _LIB = lib
     return lib

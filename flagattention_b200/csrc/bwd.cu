@@ -124,6 +124,7 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
   kv.args.out1_sb = p->dk.stride[0]; kv.args.out1_sh = p->dk.stride[1]; kv.args.out1_sr = p->dk.stride[2];
   kv.args.out2 = p->dv.ptr;
   kv.args.out2_sb = p->dv.stride[0]; kv.args.out2_sh = p->dv.stride[1]; kv.args.out2_sr = p->dv.stride[2];
+  kv.args.out2_accumulate = p->dv_accumulate != 0 ? 1 : 0;
   // Results leave through TMA stores when the output tensors can be described by tensor maps.
   kv.tmO1 = kv.tmA1; kv.tmO2 = kv.tmA1;
   kv.args.out_tma = (encode_tmap_4d(&kv.tmO1, p->dk, 2, p->B, p->Hkv, p->N, D, TileCfg<D>::CHUNK, 128,

@@ -63,6 +63,7 @@ struct BwdArgs {
   int32_t* status;
   float* dq_acc;        // FUSED: [B, Hq, M, D] fp32, zero before the launch
   int out_tma;          // the 16-bit results leave through shared memory and TMA stores (tmO1, tmO2)
+  int out2_accumulate;  // MODE_KV: out2 (dV) already holds a 16-bit gradient that this pass adds to
 };
 
 template <int D, int MODE, bool FUSED = false>
@@ -667,6 +668,27 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
 #pragma unroll
           for (int i = 0; i < NC; ++i) o[i] = 0u;
         }
+#pragma unroll
+        for (int i = 0; i < NC; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
+        if constexpr (MODE == MODE_KV) {
+          // dV on top of a gradient that is already there (second region of piecewise attention):
+          // added in fp32, rounded once.
+          if (acc == 1 && args.out2_accumulate && row < args.N) {
+            const uint16_t* prev = static_cast<const uint16_t*>(args.out2) + b * args.out2_sb + hk * args.out2_sh +
+                                   static_cast<int64_t>(row) * args.out2_sr + wg * NC;
+#pragma unroll
+            for (int x = 0; x < NC; x += 8) {
+              const uint4 pv = *reinterpret_cast<const uint4*>(prev + x);
+              const uint32_t w[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = unpack2<BF16>(w[i]);
+                o[x + 2 * i] = __float_as_uint(__uint_as_float(o[x + 2 * i]) + f.x);
+                o[x + 2 * i + 1] = __float_as_uint(__uint_as_float(o[x + 2 * i + 1]) + f.y);
+              }
+            }
+          }
+        }
         const uint32_t tile = smem_u32(sA + acc * Cfg::TILE_BYTES);
 #pragma unroll
         for (int x = 0; x < NC; x += 8) {
@@ -674,10 +696,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
           const uint32_t row_addr = tile + (c / Cfg::CHUNK) * Cfg::CHUNK_BYTES + row_local * Cfg::ROW_BYTES;
           const uint32_t swz = (row_addr >> 7) & (Cfg::ROW_BYTES / 16 - 1);
           const uint32_t dst = row_addr + (((static_cast<uint32_t>(c % Cfg::CHUNK) >> 3) ^ swz) << 4);
-          const uint32_t v0 = pack2<BF16>(__uint_as_float(o[x + 0]) * scale, __uint_as_float(o[x + 1]) * scale);
-          const uint32_t v1 = pack2<BF16>(__uint_as_float(o[x + 2]) * scale, __uint_as_float(o[x + 3]) * scale);
-          const uint32_t v2 = pack2<BF16>(__uint_as_float(o[x + 4]) * scale, __uint_as_float(o[x + 5]) * scale);
-          const uint32_t v3 = pack2<BF16>(__uint_as_float(o[x + 6]) * scale, __uint_as_float(o[x + 7]) * scale);
+          const uint32_t v0 = pack2<BF16>(__uint_as_float(o[x + 0]), __uint_as_float(o[x + 1]));
+          const uint32_t v1 = pack2<BF16>(__uint_as_float(o[x + 2]), __uint_as_float(o[x + 3]));
+          const uint32_t v2 = pack2<BF16>(__uint_as_float(o[x + 4]), __uint_as_float(o[x + 5]));
+          const uint32_t v3 = pack2<BF16>(__uint_as_float(o[x + 6]), __uint_as_float(o[x + 7]));
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
                        : "memory");
         }
@@ -731,11 +753,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUt
             for (int i = 0; i < 8; ++i) o[i] = 0u;
           }
           if (valid) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(o[i]) * scale;
+            if (MODE == MODE_KV && acc == 1 && args.out2_accumulate) {
+              const uint4 pv = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(out) + off + c);
+              const uint32_t w[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 g = unpack2<BF16>(w[i]);
+                f[2 * i] += g.x;
+                f[2 * i + 1] += g.y;
+              }
+            }
             uint4 v;
-            v.x = pack2<BF16>(__uint_as_float(o[0]) * scale, __uint_as_float(o[1]) * scale);
-            v.y = pack2<BF16>(__uint_as_float(o[2]) * scale, __uint_as_float(o[3]) * scale);
-            v.z = pack2<BF16>(__uint_as_float(o[4]) * scale, __uint_as_float(o[5]) * scale);
-            v.w = pack2<BF16>(__uint_as_float(o[6]) * scale, __uint_as_float(o[7]) * scale);
+            v.x = pack2<BF16>(f[0], f[1]);
+            v.y = pack2<BF16>(f[2], f[3]);
+            v.z = pack2<BF16>(f[4], f[5]);
+            v.w = pack2<BF16>(f[6], f[7]);
             *reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + off + c) = v;
           }
         }

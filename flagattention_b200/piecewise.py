@@ -94,21 +94,20 @@ class PiecewiseAttentionFunction(torch.autograd.Function):
             unfused = _lib.BWD_STAGE_UNFUSED if torch.are_deterministic_algorithms_enabled() else 0
             grads = []
             stages = _lib.BWD_STAGE_ALL  # the second call reuses the statistics the first one prepared
+            dv = torch.empty((B, H, N, D), dtype=v.dtype, device=device)
             for (q, k), (dmin, dmax) in zip(((q1, k1), (q2, k2)), _bands(ctx.w, ctx.causal)):
                 dq = torch.empty((B, H, M, D), dtype=q.dtype, device=device)
                 dk = torch.empty((B, H, N, D), dtype=k.dtype, device=device)
-                dv = torch.empty((B, H, N, D), dtype=v.dtype, device=device)
                 bp = _lib.BwdParams(
                     _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), _lib.tensor4(do),
                     _lib.tensor4(dq), _lib.tensor4(dk), _lib.tensor4(dv),
                     L.data_ptr(), delta.data_ptr(), workspace.data_ptr(),
                     B, H, H, M, N, D, dt, dt, int(ctx.causal), float(ctx.sm_scale), 0.0, 0, 0, status.data_ptr(),
-                    1, dmin, dmax)
+                    1, dmin, dmax, None, int(bool(grads)))   # the far region's dV is added onto the near one's
                 _lib.check(lib.b200attn_bwd_stages(bp, stream, stages | unfused), "b200attn_bwd_stages")
-                grads.append((dq, dk, dv))
+                grads.append((dq, dk))
                 stages = _lib.BWD_STAGE_KV | _lib.BWD_STAGE_Q
-            (dq1, dk1, dv_near), (dq2, dk2, dv_far) = grads
-            dv = dv_near + dv_far  # (one kernel; torch adds 16-bit tensors in fp32 and rounds once)
+            (dq1, dk1), (dq2, dk2) = grads
         return dq1, dk1, dq2, dk2, dv, None, None, None
 
 

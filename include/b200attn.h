@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define B200ATTN_ABI_VERSION 2
+#define B200ATTN_ABI_VERSION 3
 
 enum {
   B200ATTN_OK = 0,
@@ -130,6 +130,9 @@ typedef struct {
   int32_t* status;
   int32_t band, dist_min, dist_max; /* visibility band as in b200attn_fwd_params */
   const uint32_t* keep_mask;        /* cache written by b200attn_fwd for the same call, or NULL */
+  int32_t dv_accumulate;            /* != 0: dv already holds a gradient (16-bit); this call's dV is added to it in
+                                       fp32 and the sum rounded once. Piecewise attention's two (q, k) pairs share
+                                       one v (`piecewise.py:132-180` accumulates both regions into one dv) */
 } b200attn_bwd_params;
 
 size_t b200attn_bwd_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t M, int32_t N,

@@ -2,6 +2,7 @@
 reference's tests (tests/flag_attn/test_piecewise_attention.py:27-160), plus the visibility band of the
 C ABI that it is built on."""
 import itertools
+import math
 
 import pytest
 import torch
@@ -106,7 +107,6 @@ def test_degenerate_thresholds(w):
 @pytest.mark.parametrize("D", [64, 128])
 def test_band_mask_through_the_c_abi(dmin, dmax, D):
     """b200attn_fwd / b200attn_bwd with a visibility band (a sliding window) against masked dense math."""
-    import math
     B, H, M, N = 1, 2, 400, 520
     dtype = torch.bfloat16
     g = torch.Generator(device=device()).manual_seed(5)
@@ -183,3 +183,50 @@ def test_merge_partial_store_equals_merge_then_round(D, dtype):
     torch.cuda.synchronize()
     assert torch.equal(out, ref_o.to(dtype))
     assert torch.equal(got_l, ref_l)
+
+
+@pytest.mark.parametrize("D,N,out_contig", [(128, 1000, True), (64, 777, True), (32, 300, True), (128, 520, False)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_dv_accumulate_adds_in_fp32_and_rounds_once(D, N, out_contig, dtype):
+    """`dv_accumulate`: the backward adds its dV onto the 16-bit gradient already in the dv buffer (what the
+    second region of piecewise attention does, `piecewise.py:132-180` sums both regions into one dv). The
+    result must be round(float(previous) + fp32 dV): compared with a plain call's dV it may differ from
+    round(previous + round(dV)) by one rounding of dV only. dQ and dK are untouched by the flag. The last
+    case has dv in the transposed layout, which the kernel stores from registers instead of through TMA."""
+    B, H, M = 2, 3, 333
+    g = torch.Generator(device=device()).manual_seed(11)
+    q, do = (torch.randn(B, H, M, D, device=device(), dtype=dtype, generator=g) for _ in range(2))
+    k, v = (torch.randn(B, H, N, D, device=device(), dtype=dtype, generator=g) for _ in range(2))
+    prev = torch.randn(B, H, N, D, device=device(), dtype=dtype, generator=g)
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    dt = _lib.dtype_code(dtype)
+    status = torch.zeros(1, dtype=torch.int32, device=device())
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, M, dtype=torch.float32, device=device())
+    fp = _lib.FwdParams(_lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), lse.data_ptr(), B, H, H, M, N, D,
+                        dt, dt, 1, 1 / math.sqrt(D), 0.0, 0, 0, status.data_ptr())
+    _lib.check(lib.b200attn_fwd(fp, st), "fwd")
+    results = []
+    for accumulate in (0, 1):
+        dq, dk = torch.empty_like(q), torch.empty_like(k)
+        dv = (prev.clone() if out_contig else prev.transpose(1, 2).contiguous().transpose(1, 2)) if accumulate \
+            else torch.empty_like(v)
+        delta = torch.empty_like(lse)
+        ws = torch.empty(max(lib.b200attn_bwd_workspace_bytes(B, H, H, M, N, D), 4) // 4, dtype=torch.float32,
+                         device=device())
+        bp = _lib.BwdParams(_lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v), _lib.tensor4(o), _lib.tensor4(do),
+                            _lib.tensor4(dq), _lib.tensor4(dk), _lib.tensor4(dv), lse.data_ptr(), delta.data_ptr(),
+                            ws.data_ptr(), B, H, H, M, N, D, dt, dt, 1, 1 / math.sqrt(D), 0.0, 0, 0, status.data_ptr(),
+                            0, 0, 0, None, accumulate)
+        _lib.check(lib.b200attn_bwd_stages(bp, st, _lib.BWD_STAGE_ALL | _lib.BWD_STAGE_UNFUSED), "bwd")
+        results.append((dq, dk, dv))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    (dq0, dk0, dv0), (dq1, dk1, dv1) = results
+    assert torch.equal(dq0, dq1) and torch.equal(dk0, dk1)
+    want = prev.float() + dv0.float()            # dv0 = round(fp32 dV): within half an ulp of dV
+    ulp = torch.finfo(dtype).eps
+    tol = (dv0.float().abs() * ulp / 2 + want.abs() * ulp / 2 + 1e-6)
+    assert bool(((dv1.float() - want).abs() <= tol * 1.01).all())
+    assert not torch.equal(dv1, prev)

@@ -20,7 +20,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(str(_lib.lib_path()))
     for name in declared:
         assert hasattr(lib, name), name
-    assert _lib.load().b200attn_abi_version() == 2
+    assert _lib.load().b200attn_abi_version() == 3
 
 
 def test_invalid_arguments_are_rejected_before_any_cuda_call():
