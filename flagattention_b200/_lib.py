@@ -19,7 +19,7 @@ _DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
 ERROR_NAMES = {0: "OK", -1: "EINVAL", -2: "EUNSUPPORTED", -3: "ECUDA", -4: "ETIMEOUT"}
 
 # Stage bits of b200attn_bwd_stages (include/b200attn.h).
-BWD_STAGE_PREP, BWD_STAGE_KV, BWD_STAGE_Q, BWD_STAGE_ALL, BWD_STAGE_UNFUSED = 1, 2, 4, 7, 8
+BWD_STAGE_PREP, BWD_STAGE_KV, BWD_STAGE_Q, BWD_STAGE_ALL, BWD_STAGE_UNFUSED, BWD_STAGE_ACC_ZEROED = 1, 2, 4, 7, 8, 16
 # Open ends of the visibility band (FwdParams.dist_min / dist_max).
 BAND_OPEN_MIN, BAND_OPEN_MAX = -(2 ** 31), 2 ** 31 - 1
 

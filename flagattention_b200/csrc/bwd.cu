@@ -160,7 +160,7 @@ static int run_bwd(const b200attn_bwd_params* p, float2* stats, cudaStream_t str
     const int64_t n_acc = static_cast<int64_t>(p->B) * p->Hq * p->M * D;
     if (stages & B200ATTN_BWD_STAGE_KV) {
       // (cleared by the preprocess when that ran in this call)
-      if (!(stages & B200ATTN_BWD_STAGE_PREP))
+      if (!(stages & (B200ATTN_BWD_STAGE_PREP | B200ATTN_BWD_STAGE_ACC_ZEROED)))
         B200ATTN_CUDA_OK(cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(n_acc) * sizeof(float), stream));
       kv.fused = true;
       kv.args.dq_acc = dq_acc;

@@ -144,13 +144,17 @@ int b200attn_bwd(const b200attn_bwd_params* p, void* stream);
  * kernel; KV and Q need the scratch PREP wrote. At D = 128 and 64 the KV stage is a fused pass that also
  * accumulates dQ in fp32 (in the workspace, by global reductions, so dQ is reproducible only up to
  * fp32 summation order) and the Q stage is the conversion of that accumulator; adding UNFUSED
- * selects the two separate kernels instead. No counterpart in the reference. */
+ * selects the two separate kernels instead. The fused pass needs its accumulator
+ * cleared: PREP clears it when it runs in the same call, otherwise the call clears it first unless
+ * ACC_ZEROED says the caller has done so. No counterpart in the reference. */
 enum {
   B200ATTN_BWD_STAGE_PREP = 1,
   B200ATTN_BWD_STAGE_KV = 2,
   B200ATTN_BWD_STAGE_Q = 4,
   B200ATTN_BWD_STAGE_ALL = 7,
-  B200ATTN_BWD_STAGE_UNFUSED = 8
+  B200ATTN_BWD_STAGE_UNFUSED = 8,
+  B200ATTN_BWD_STAGE_ACC_ZEROED = 16  /* the fp32 dQ accumulator (workspace bytes [B*Hq*roundup(M,128)*8,
+                                         + B*Hq*M*D*4)) is already zero */
 };
 int b200attn_bwd_stages(const b200attn_bwd_params* p, void* stream, int32_t stages);
 
