@@ -289,7 +289,7 @@ def triton_reference(cfg, q, k, v, do, iters=10):
     `o.backward(do, retain_graph=True)`)."""
     ref_dir = ROOT / "baseline" / "_ref"
     if not (ref_dir / "flag_attn").is_dir():
-        return {"unavailable": "baseline/_ref is not installed (recipe in BASELINE.md)"}
+        return {"unavailable": "baseline/_ref is not installed (python -m pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <writable copy of the reference checkout>)"}
     if str(ref_dir) not in sys.path:
         sys.path.append(str(ref_dir))
     try:

@@ -13,7 +13,8 @@ if str(ROOT) not in sys.path:
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
-# The unmodified reference, installed by the recipe in BASELINE.md into the git-ignored baseline/_ref
+# The unmodified reference, installed into the git-ignored baseline/_ref with
+#   python -m pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <writable copy of the reference checkout>
 # (it is not product source). Only the same-GPU A/B tests import it; absent, they skip with a reason.
 REFERENCE_INSTALL = ROOT / "baseline" / "_ref"
 if (REFERENCE_INSTALL / "flag_attn").is_dir() and str(REFERENCE_INSTALL) not in sys.path:

@@ -1,6 +1,7 @@
 """Same-GPU A/B against the reference's own Triton ``flash_attention``.
 
-The unmodified reference is installed under ``baseline/_ref`` (git-ignored; recipe in BASELINE.md).
+The unmodified reference is installed under ``baseline/_ref`` (git-ignored) with
+``python -m pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <writable copy of the reference checkout>``.
 On identical seeded inputs, and with the default CUDA generator put in the same state before each call
 (so both draw the same Philox ``(seed, offset)`` and hence the same dropout decisions), every result of
 this library must lie within
@@ -31,7 +32,7 @@ def _reference():
     try:
         return importlib.import_module("flag_attn")
     except Exception as exc:  # noqa: BLE001
-        pytest.skip(f"reference install baseline/_ref not importable ({exc!r}); see BASELINE.md for the recipe")
+        pytest.skip(f"reference install baseline/_ref not importable ({exc!r}); install it with pip --target baseline/_ref")
 
 
 def _err(x, ref):

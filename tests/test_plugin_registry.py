@@ -93,7 +93,7 @@ def _real_reference_root():
 
 
 @pytest.mark.skipif(_real_reference_root() is None,
-                    reason="no reference package: set FLAG_ATTN_REF or install baseline/_ref (BASELINE.md)")
+                    reason="no reference package: set FLAG_ATTN_REF or pip install the reference with --target baseline/_ref")
 def test_install_into_the_reference_registry_itself(monkeypatch):
     """The same round trip through the reference's real facade and registry
     (`src/flag_attn/__init__.py:123-135`, `runtime/backend/op_registry.py:18-60`). No kernel runs: the
