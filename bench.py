@@ -811,7 +811,10 @@ def main():
     if dist is not None and args.config == DEFAULT_CONFIG and args.shard == "auto":
         del q, k, v, do, host_in, host_out, outs
         torch.cuda.empty_cache()
-        heads, ring_rec = c5_sharded_legs(rank, world, device, dist)
+        try:
+            heads, ring_rec = c5_sharded_legs(rank, world, device, dist)
+        except Exception as exc:  # noqa: BLE001  (the headline record above must survive a failure here)
+            heads = ring_rec = {"error": repr(exc)[:300]}
         if result is not None:
             result["c5_heads"], result["c5_ring"] = heads, ring_rec
     if dist is not None:
