@@ -5,10 +5,6 @@ grouped heads, bands, dropout, transposed layouts) and every head dimension is c
 checked against the oracle with the reference's acceptance rule
 (tests/flag_attn/test_flash_attention.py:116-124), and against a launch of one CTA per item where
 the two must agree bit for bit."""
-import os
-import subprocess
-import sys
-
 import pytest
 import torch
 
@@ -69,9 +65,11 @@ def test_forward_many_items_dropout(D):
 
 
 @pytest.mark.parametrize("dist_min,dist_max", [(0, 200), (-50, 300), (100, 1 << 30)])
-def test_forward_many_items_band(dist_min, dist_max):
-    """A visibility band through the C entry point: items whose first K/V tile is not tile 0."""
-    B, Hq, Hk, M, N, D, dtype = 4, 40, 8, 900, 1100, 64, torch.bfloat16
+@pytest.mark.parametrize("D", [64, 128])
+def test_forward_many_items_band(dist_min, dist_max, D):
+    """A visibility band through the C entry point: items whose first K/V tile is not tile 0 (D = 128 takes
+    the 64-key softmax pipeline, D = 64 the 128-key one)."""
+    B, Hq, Hk, M, N, dtype = 4, 40, 8, 900, 1100, torch.bfloat16
     q, k, v, _ = make_qkv(B, Hq, Hk, M, N, D, dtype, "BHTD", 1.0, seed=8)
     lib = _lib.load()
     o = torch.empty_like(q)
@@ -98,34 +96,33 @@ def test_forward_many_items_band(dist_min, dist_max):
     assert_2x_rule("o", o, formula(False), formula(True))
 
 
-_CHILD = r"""
-import sys, torch
-sys.path.insert(0, sys.argv[1])
-from flagattention_b200 import flash_attention, check_device_status
-out = []
-for (B, Hq, Hk, M, N, D, causal, p) in [(8, 16, 16, 700, 700, 128, True, 0.0), (4, 32, 8, 1000, 1000, 64, False, 0.0),
-                                       (4, 48, 12, 600, 777, 64, True, 0.2), (16, 12, 12, 300, 1500, 16, True, 0.0)]:
-    g = torch.Generator(device="cuda").manual_seed(3)
-    q = torch.randn(B, Hq, M, D, device="cuda", dtype=torch.bfloat16, generator=g)
-    k = torch.randn(B, Hk, N, D, device="cuda", dtype=torch.bfloat16, generator=g)
-    v = torch.randn(B, Hk, N, D, device="cuda", dtype=torch.bfloat16, generator=g)
-    torch.manual_seed(77)
-    o, lse = flash_attention(q, k, v, causal, dropout_p=p, return_log_normalizer=True)[:2]
-    out += [o.cpu(), lse.cpu()]
-check_device_status()
-torch.save(out, sys.argv[2])
-"""
-
-
-def test_chained_items_match_one_cta_per_item(tmp_path):
-    """The same launches with the chaining switched off (one CTA per item) give identical bits: the
-    per-item arithmetic does not depend on which CTA runs the item or what it ran before."""
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    outs = []
-    for mode in ("1", "0"):
-        path = tmp_path / f"out{mode}.pt"
-        env = dict(os.environ, B200ATTN_FWD_PERSISTENT=mode)
-        subprocess.run([sys.executable, "-c", _CHILD, root, str(path)], check=True, env=env, timeout=600)
-        outs.append(torch.load(path))
-    for a, b in zip(*outs):
-        assert torch.equal(a, b)
+@pytest.mark.parametrize("B,Hq,Hk,M,N,D,causal,p", [
+    (8, 16, 16, 700, 700, 128, True, 0.0), (4, 32, 8, 1000, 1000, 64, False, 0.0),
+    (4, 48, 12, 600, 777, 64, True, 0.2), (16, 12, 12, 300, 1500, 16, True, 0.0),
+    (6, 32, 8, 900, 1300, 128, False, 0.0)])
+def test_chained_items_match_one_cta_per_item(B, Hq, Hk, M, N, D, causal, p):
+    """A launch over the whole batch has more work items than SMs, so every CTA walks several of them; a
+    launch over one batch element has fewer and runs one CTA per item. Both must give identical bits: the
+    per-item arithmetic does not depend on which CTA runs the item or on what that CTA ran before."""
+    sms = torch.cuda.get_device_properties(device()).multi_processor_count
+    per_batch = Hq * -(-M // 256)
+    assert B * per_batch > sms >= per_batch
+    g = torch.Generator(device=device()).manual_seed(3)
+    q = torch.randn(B, Hq, M, D, device=device(), dtype=torch.bfloat16, generator=g)
+    k = torch.randn(B, Hk, N, D, device=device(), dtype=torch.bfloat16, generator=g)
+    v = torch.randn(B, Hk, N, D, device=device(), dtype=torch.bfloat16, generator=g)
+    torch.cuda.manual_seed(77)
+    o, lse, _, seed, offset = flash_attention(q, k, v, causal, dropout_p=p, return_log_normalizer=True,
+                                              return_seed_offset=True)
+    for b in (0, B - 1):
+        if p > 0:
+            # element (b, h, m, n) of the whole problem draws counter offset + ((b*Hq + h)*M + m)*N + n:
+            # put the generator where the slice's own numbering reproduces those counters
+            st = torch.cuda.default_generators[device().index].get_state()
+            st.view(torch.int64)[0] = seed
+            st.view(torch.int64)[1] = offset + b * Hq * M * N
+            torch.cuda.default_generators[device().index].set_state(st)
+        o1, lse1 = flash_attention(q[b:b + 1], k[b:b + 1], v[b:b + 1], causal, dropout_p=p,
+                                   return_log_normalizer=True)[:2]
+        assert torch.equal(o1, o[b:b + 1]) and torch.equal(lse1, lse[b:b + 1])
+    check_device_status()
