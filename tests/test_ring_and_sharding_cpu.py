@@ -99,7 +99,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_ring_loop_world2_gloo(world):
     torch.manual_seed(0)
     B, Hq, Hk, S, D = 1, 4, 2, 64 * world // 2, 16
