@@ -35,6 +35,7 @@ After that the ranks also run the 32k-token forward configuration split two ways
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import math
 import os
@@ -107,10 +108,11 @@ def ncu_traffic(workload: str, kernel: str, batch: int):
 
 # ------------------------------------------------------------------ clocks sampling
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    """Samples nvidia-smi clocks / throttle reasons of one GPU every 50 ms; ``stop(t0, t1)`` keeps the
+    samples whose time stamp lies inside the timed region [t0, t1] (``datetime`` values of this host)."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_power_cap,timestamp")
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
@@ -126,7 +128,7 @@ class ClockSampler:
             [exe, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i",
              str(self.gpu_index)], stdout=self.tmp, stderr=subprocess.DEVNULL)
 
-    def stop(self):
+    def stop(self, t0=None, t1=None):
         if self.proc is None:
             return None
         self.proc.terminate()
@@ -143,6 +145,20 @@ class ClockSampler:
         os.unlink(self.tmp.name)
         if not rows:
             return None
+        n_all = len(rows)
+        if t0 is not None and t1 is not None:
+            def stamp(r):
+                try:
+                    return datetime.datetime.strptime(r[7], "%Y/%m/%d %H:%M:%S.%f")
+                except (ValueError, IndexError):
+                    return None
+            inside = [r for r in rows if (ts := stamp(r)) is not None and t0 <= ts <= t1]
+            if not inside:      # a region shorter than the sampling period: the samples next to it
+                near = [r for r in rows if (ts := stamp(r)) is not None
+                        and t0 - datetime.timedelta(milliseconds=60) <= ts <= t1 + datetime.timedelta(milliseconds=60)]
+                inside = near
+            if inside:
+                rows = inside
         sm = []
         for r in rows:
             try:
@@ -158,8 +174,10 @@ class ClockSampler:
             sm_max = float(rows[0][1])
         except ValueError:
             sm_max = None
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": sm_max,
-                "reasons": reasons, "samples": len(rows)}
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_mhz_min": min(sm) if sm else None,
+                "sm_max_mhz": sm_max, "reasons": reasons, "samples": len(rows), "samples_taken": n_all,
+                "note": "samples stamped inside the timed region; the driver's clock reading lags the load by "
+                        "about 0.1 s"}
 
 
 # ------------------------------------------------------------------ workload
@@ -646,7 +664,7 @@ def main():
     # ---- device-resident timing --------------------------------------------------------------
     step = (lambda: ring_step()) if ring_step is not None else (lambda: run_step(cfg, q, k, v, do))
     # The clock sampler starts before the warm-up (nvidia-smi takes a few hundred ms to come up) and
-    # runs through the timed region; warm-up steps are the same work, so every sample is under load.
+    # runs through the timed region; only the samples stamped inside the timed region are reported.
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
@@ -657,14 +675,16 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if ring_step is not None:
         ring.LAUNCHES = 0
+    wall0 = datetime.datetime.now()
     e0.record()
     for _ in range(K):
         step()
     e1.record()
     ring_launches = ring.LAUNCHES if ring_step is not None else 0
     barrier()
+    wall1 = datetime.datetime.now()
     ms_total = e0.elapsed_time(e1)
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(wall0, wall1) if sampler else None
     status_mod.check_device_status(device)   # no kernel of the timed region gave up on a wait
 
     # ---- end-to-end timing: host buffers, copies inside the timed region ----------------------
