@@ -23,14 +23,14 @@ static void set_item_order(FwdArgs& a, int64_t grid_heads) {
   a.div_splits = FastDiv::make(a.num_splits);
 }
 
-// 16-bit outputs leave through shared memory and TMA stores; when the output cannot be described by
-// a tensor map the kernel stores from registers instead.
+// 16-bit outputs leave through shared memory and TMA stores (one box of 32 rows per softmax warp); when
+// the output cannot be described by a tensor map the kernel stores from registers instead.
 template <int D>
 static void make_o_tmap(const b200attn_fwd_params* p, FwdLaunch& L) {
   using Cfg = TileCfg<D>;
   L.args.o_tma = 0;
   if (p->o_dtype == B200ATTN_F32) return;
-  if (encode_tmap_4d(&L.tmO, p->o, 2, p->B, p->Hq, p->M, D, Cfg::CHUNK, Cfg::BLOCK, Cfg::TMA_SWZ, "o") ==
+  if (encode_tmap_4d(&L.tmO, p->o, 2, p->B, p->Hq, p->M, D, Cfg::CHUNK, 32, Cfg::TMA_SWZ, "o") ==
       B200ATTN_OK) {
     L.args.o_tma = 1;
   }

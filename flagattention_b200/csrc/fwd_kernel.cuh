@@ -175,8 +175,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   uint64_t* p_half = s_full + 4;            // [2 tiles][2 halves] (SPLIT64: P of buffer 0 / 1)
   uint64_t* o_full = p_half + 4;            // [2]
   uint64_t* q_empty = o_full + 2;           // [2]
-  uint64_t* o_sync = q_empty + 2;           // [2] the four warps of a tile meet here around the output staging
-  uint64_t* pv_done = o_sync + 2;           // [2] SPLIT64: every P V issued so far for the tile has completed
+  uint64_t* pv_done = q_empty + 2;          // [2] SPLIT64: every P V issued so far for the tile has completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -260,7 +259,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       mbar_init(&p_half[2 * t + 1], 128);
       mbar_init(&o_full[t], 1);
       mbar_init(&q_empty[t], 1);
-      mbar_init(&o_sync[t], 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -635,16 +633,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     uint32_t s_par = 0, o_par = 0;  // phases of s_full[t] and o_full[t], running on across work items
     uint32_t s_par1 = 0;            // SPLIT64: phase of the second score buffer's barrier (s_par: the first)
     uint32_t pv_idx = 0;            // SPLIT64: items of this tile so far with two or more sub-steps = phase of pv_done
-    uint32_t sync_par = 0;          // and of o_sync[t]
-    // Meeting point of the tile's four warps (an mbarrier rather than bar.sync so that the wait is
-    // bounded like every other wait of the kernel).
-    auto tile_sync = [&]() -> bool {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&o_sync[t]);  // one arrival per warp, ordered after its lanes' writes
-      const bool w = wait(&o_sync[t], sync_par);
-      sync_par ^= 1;
-      return w;
-    };
     bool ok = true;
 
     for (int k = 0; ok; ++k) {
@@ -975,16 +963,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
     };
     if (args.o_tma) {
-      // 16-bit output: each thread scales its row, the tile's four warps lay one [128 x CHUNK] box
-      // out in shared memory in the swizzled layout of the output tensor map, and one thread stores
-      // the box with TMA (rows past M are clipped by the tensor map). The direct path below writes
-      // 32 rows x 16 bytes per warp instruction, which costs several microseconds per tile.
+      // 16-bit output: each thread scales its row, every warp lays its [32 x CHUNK] box out in shared
+      // memory in the swizzled layout of the output tensor map (whose box is 32 rows, so that a warp
+      // depends on no other warp here) and its first lane stores the box with TMA (rows past M are
+      // clipped by the tensor map). The direct path below writes 32 rows x 16 bytes per warp
+      // instruction, which costs several microseconds per tile.
       tc_fence_after();
       const bool empty = (nt == 0) || (m_run == -INFINITY) || !(l_run > 0.f);
       float inv = empty ? 0.f : 1.0f / l_run;
       if constexpr (DROPOUT) inv *= args.drop.inv_keep;
-      const bool tile_live = m0 + t * BLOCK < args.M;  // uniform over the tile's four warps
-      const bool issuer = (warp & 3) == 0 && lane == 0;
+      const int m_warp = m0 + t * BLOCK + (warp & 3) * 32;   // first query row of this warp's box
+      const bool tile_live = m_warp < args.M;                // warp-uniform
+      const bool issuer = lane == 0;
       uint8_t* stage = sO + t * Cfg::CHUNK_BYTES;
       auto stage_chunk = [&](const int c) {
           uint32_t o[Cfg::CHUNK];
@@ -996,9 +986,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
             for (int i = 0; i < Cfg::CHUNK; ++i) o[i] = 0u;
           }
-          // the previous store from this buffer has been read out of shared memory
+          // this warp's previous store from the buffer has been read out of shared memory
           if (issuer) tma_store_wait_read();
-          if (!tile_sync()) { if (ok) fail(ST_WAIT_SOFTMAX); ok = false; }
+          __syncwarp();
           const uint32_t row_addr = smem_u32(stage) + row * Cfg::ROW_BYTES;
           const uint32_t swz = (row_addr >> 7) & (Cfg::ROW_BYTES / 16 - 1);  // 16-byte unit XOR of the swizzle
 #pragma unroll
@@ -1017,9 +1007,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                          : "memory");
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          if (!tile_sync()) { if (ok) fail(ST_WAIT_SOFTMAX); ok = false; }
+          __syncwarp();
           if (issuer && ok) {
-            tma_store_4d(&tmO, stage, c * Cfg::CHUNK, m0 + t * BLOCK, h, b);
+            tma_store_4d(&tmO, stage + (warp & 3) * 32 * Cfg::ROW_BYTES, c * Cfg::CHUNK, m_warp, h, b);
             tma_store_commit();
           }
       };
@@ -1087,7 +1077,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
     }  // work items
     // Shared memory must outlive the reads of the last output stores.
-    if (args.o_tma && (warp & 3) == 0 && lane == 0) tma_store_wait_all();
+    if (args.o_tma && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
