@@ -703,13 +703,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         // columns that every row of the warp sees in full are left alone.
         const int hi_rel = lim - n0, lo_rel = lo - n0;
         const int hi_min = __reduce_min_sync(0xffffffffu, hi_rel);
-        const int lo_max = __reduce_max_sync(0xffffffffu, lo_rel);
+        if (args.d_max >= BAND_INF) {
+          // plain causal masking (no far edge): one comparison per score
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          if (32 * c + 32 > hi_min || 32 * c < lo_max) {
+          for (int c = 0; c < 2; ++c) {
+            if (32 * c + 32 > hi_min) {
 #pragma unroll
-            for (int i = 32 * c; i < 32 * c + 32; ++i)
-              if (i >= hi_rel || i < lo_rel) s[i] = 0xff800000u;  // -inf
+              for (int i = 32 * c; i < 32 * c + 32; ++i)
+                if (i >= hi_rel) s[i] = 0xff800000u;  // -inf
+            }
+          }
+        } else {
+          const int lo_max = __reduce_max_sync(0xffffffffu, lo_rel);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            if (32 * c + 32 > hi_min || 32 * c < lo_max) {
+#pragma unroll
+              for (int i = 32 * c; i < 32 * c + 32; ++i)
+                if (i >= hi_rel || i < lo_rel) s[i] = 0xff800000u;  // -inf
+            }
           }
         }
       }
@@ -849,13 +861,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         // pipe, which the softmax already loads with its conversions and maxima).
         const int hi_rel = lim - jg * BLOCK, lo_rel = lo - jg * BLOCK;
         const int hi_min = __reduce_min_sync(0xffffffffu, hi_rel);
-        const int lo_max = __reduce_max_sync(0xffffffffu, lo_rel);
+        if (args.d_max >= BAND_INF) {
+          // plain causal masking or the end of the keys (no far edge): one comparison per score
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (32 * c + 32 > hi_min || 32 * c < lo_max) {
+          for (int c = 0; c < 4; ++c) {
+            if (32 * c + 32 > hi_min) {
 #pragma unroll
-            for (int i = 32 * c; i < 32 * c + 32; ++i)
-              if (i >= hi_rel || i < lo_rel) s[i] = 0xff800000u;  // -inf
+              for (int i = 32 * c; i < 32 * c + 32; ++i)
+                if (i >= hi_rel) s[i] = 0xff800000u;  // -inf
+            }
+          }
+        } else {
+          const int lo_max = __reduce_max_sync(0xffffffffu, lo_rel);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (32 * c + 32 > hi_min || 32 * c < lo_max) {
+#pragma unroll
+              for (int i = 32 * c; i < 32 * c + 32; ++i)
+                if (i >= hi_rel || i < lo_rel) s[i] = 0xff800000u;  // -inf
+            }
           }
         }
       }
